@@ -21,6 +21,13 @@ extern "C" {
 enum { MRS_SEQ_BF16 = 1, MRS_SEQ_F32 = 2 };
 enum { MRS_SEQ_ACT_NONE = 0, MRS_SEQ_ACT_SILU = 1, MRS_SEQ_ACT_GELU_TANH = 2, MRS_SEQ_ACT_SIGMOID = 3, MRS_SEQ_ACT_GELU_ERF = 4,
        MRS_SEQ_ACT_RELU_SQ = 5 };
+/* How a gated feed-forward joins its two halves.  act != MRS_SEQ_GLU_CAPPED: act(gate) * up.  MRS_SEQ_GLU_CAPPED:
+ * g = min(gate, limit), u = clamp(up, -limit, limit), result g * sigmoid(slope * g) * (u + shift). */
+enum { MRS_SEQ_GLU_CAPPED = 100 };
+typedef struct {
+  int act;
+  float limit, slope, shift;
+} mrs_seq_glu_rule;
 
 /* ---- residual streams ------------------------------------------------------------------------------ */
 /* streams[t][s][:] = table[ids[t]][:] for every stream s (streams f32 [n_tok, n_streams, width]). */
@@ -50,11 +57,47 @@ int mrs_seq_residual_tanh_norm(float *x, const void *y, int dtype, const float *
                                const float *post_bias, const float *extra, const float *next_alpha, const float *next_weight,
                                const float *next_bias, void *next_out, int n_tok, int width, int64_t stream);
 
+/* ---- single residual with RMS norms, scaled sublayer outputs and a depth-weighted average ------------ */
+/* out[t][:] = table[ids[t]][:] * scale (f32). */
+int mrs_seq_embed_scaled(const void *table, int dtype, const int32_t *ids, float scale, float *out, int n_tok, int width,
+                         int64_t stream);
+/* One pass per token over an f32 residual, every part optional (NULL: skipped), in this order:
+ *   v = src[t] + mult * y[t]                       (y: a sublayer's output, activation type; NULL: v = src[t])
+ *   dst[t] = v                                      (dst may be src)
+ *   v = sum_(j < n_hist) mix[j] * hist[j][t]        (hist f32 [n_hist][n_tok][width] with entry stride hist_stride floats;
+ *                                                    an entry may be dst, which then already holds this token's v)
+ *   mixed[t] = v
+ *   next_out[t] = v / sqrt(mean(v^2) + eps) * next_w   (the next sublayer's input, activation type)
+ * With hist = the embedding output followed by every layer's result so far this is the depth-weighted average of
+ * DenseFormer-style models; without it, the plain pre-norm residual step with a multiplier. */
+typedef struct {
+  const float *src;
+  float *dst;
+  const void *y;
+  float mult;
+  const float *hist;
+  int64_t hist_stride;
+  int n_hist;
+  const float *mix;
+  float *mixed;
+  const float *next_w;
+  float eps;
+  void *next_out;
+  int dtype, n_tok, width;
+} mrs_seq_rms_residual_args;
+int mrs_seq_rms_residual(const mrs_seq_rms_residual_args *args, int64_t stream);
+
 /* ---- elementwise / norms --------------------------------------------------------------------------- */
 /* x[t][c] = act(x[t][c]) in place for c < cols (row stride ld) */
 int mrs_seq_activate_cols(void *x, int64_t ld, int dtype, int n_tok, int cols, int act, int64_t stream);
 /* out[t][c] = act(x[t][c]) * x[t][half + c]   (x [n_tok, 2 * half]) */
 int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream);
+/* the same with any joining rule */
+int mrs_seq_glu_join(const void *x, void *out, int dtype, int n_tok, int half, const mrs_seq_glu_rule *rule, int64_t stream);
+/* gate[t][c] = lower[c] + (1 - lower[c]) * sigmoid(raw[t][c] + bias[c]) in f32: a forget gate bounded from below.  raw is
+ * columns of an activation tensor (row stride raw_ld); gate f32 [n_tok, cols]. */
+int mrs_seq_bounded_gate(const void *raw, int64_t raw_ld, int dtype, const float *bias, const float *lower, int n_tok, int cols,
+                         float *gate, int64_t stream);
 /* Root-mean-square norm of f32 rows in `groups` equal parts, times weight, with a gate read from an activation
  * tensor (row stride gate_ld): gate_first != 0: norm(x * act(gate)) * w; else norm(x) * w * act(gate).  The result,
  * times out_scale, goes to out[t * out_ld + c]. */
@@ -79,6 +122,8 @@ int mrs_seq_ssm_steps(const void *in, int64_t in_ld, int col0, int dtype, const 
  *   S_t = a_t S_(t-1) + b_t k_t v_t^T     (S f32 [dk, dv], kept in state[slot][h])
  *   o_t = S_t^T q_t + skip[h] v_t         (o f32 [n_tok, heads * dv])
  * a_t = decay_tok[t][h] (or decay_head[h] when decay_tok is NULL), b_t = scale_tok[t][h] (1 when NULL), skip NULL: 0.
+ * decay_vec f32 [n_tok, heads, dk] (then decay_tok, decay_head and k are NULL and qk_groups == heads): every state row has
+ * its own decay and the key is its complement, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; such portions run in one pass.
  * q, k: [n_tok, qk_groups, dk] with row strides q_ld / k_ld; v: [n_tok, heads, dv] with row stride v_ld; `act` is
  * applied to q, k and v as they are read.
  * Long portions can run as n_segs segments of seg_len tokens side by side (n_segs > 1): the caller provides
@@ -97,6 +142,7 @@ typedef struct {
   float *out;
   float *seg_state, *seg_decay;
   int seg_len, n_segs;
+  const float *decay_vec;
 } mrs_seq_scan_args;
 int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream);
 
@@ -175,6 +221,8 @@ typedef struct {
   void *out;
   int64_t out_ld;
   float out_scale;
+  int64_t k_row, v_row;   /* elements between the cache rows of neighbouring slots; 0: kv_heads * dk / kv_heads * dv.  Values that
+                             are a column range of the key rows: v_cache = k_cache + first column, v_row = k_row. */
 } mrs_seq_paged_attention_args;
 int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args, int64_t stream);
 /* The long portions of a step on tensor cores (bf16, dk = dv = d of 64 or 128, q / out rows 16-byte aligned), with the same
@@ -185,6 +233,36 @@ int mrs_seq_prompt_attention(const void *q, int64_t q_ld, const void *k_cache, c
                              const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
                              int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
                              const float *sink, int64_t stream);
+/* ---- attention through a shared latent ----------------------------------------------------------------- */
+/* Per token, from the columns of one projection y (row stride y_ld, activation type), any part optional:
+ *   q_out[t] = rms_norm(y[t][q_col : q_col + q_rank]) * q_norm_w                      (the query latent, activation type)
+ *   cache[slot(t)][0 : kv_rank] = rms_norm(y[t][kv_col : kv_col + kv_rank]) * kv_norm_w   (the key/value latent)
+ *   cache[slot(t)][kv_rank : kv_rank + rot_dim] = turn(y[t][kv_col + kv_rank : ...])     (the key part all heads share)
+ * turn: entries (2i, 2i + 1), i < rot_dims / 2, rotate by cos_sin[t][i] (f32 [n_tok, rot_dims / 2, 2]); the rest pass.
+ * cache rows are cache_row elements apart.  q_rank 0: no query part; kv_rank 0: no cache part. */
+typedef struct {
+  const void *y;
+  int64_t y_ld;
+  int dtype;
+  int q_col, q_rank;
+  const float *q_norm_w;
+  void *q_out;
+  int64_t q_out_ld;
+  int kv_col, kv_rank, rot_dim, rot_dims;
+  const float *kv_norm_w;
+  const float *cos_sin;
+  float eps;
+  void *cache;
+  int64_t cache_row;
+  const int64_t *slot_of_tok;
+  int n_tok;
+} mrs_seq_latent_prepare_args;
+int mrs_seq_latent_prepare(const mrs_seq_latent_prepare_args *args, int64_t stream);
+/* out[t][h][0:dims] = in[t][h][0:dims] with entries (2i, 2i + 1), i < rot_dims / 2, rotated by cos_sin[t][i], the rest
+ * copied.  in / out: activation type, row strides in_ld / out_ld, head strides in_head / out_head (elements). */
+int mrs_seq_rotate_pairs(const void *in, int64_t in_ld, int64_t in_head, void *out, int64_t out_ld, int64_t out_head, int dtype,
+                         int heads, int dims, int rot_dims, const float *cos_sin, int n_tok, int64_t stream);
+
 /* x[r][c] *= scale for r < rows, c < cols (row stride ld) */
 int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream);
 
@@ -195,6 +273,13 @@ int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float
  * when renorm != 0).  experts / weights: [n_tok, top]. */
 int mrs_seq_moe_route(const float *logits, const float *correction, int n_tok, int n_experts, int n_groups, int keep_groups,
                       int top, int renorm, int32_t *experts, float *weights, int64_t stream);
+/* The same rule with its choices open: scores = softmax over the experts (score_fn 0) or sigmoid of each logit (1); a
+ * group's score is the sum of its group_top largest choices (1: the largest); the weights are the chosen scores
+ * (renormalised when renorm != 0) times weight_scale. */
+enum { MRS_SEQ_SCORE_SOFTMAX = 0, MRS_SEQ_SCORE_SIGMOID = 1 };
+int mrs_seq_moe_route_scored(const float *logits, const float *correction, int n_tok, int n_experts, int n_groups, int keep_groups,
+                             int top, int renorm, int score_fn, int group_top, float weight_scale, int32_t *experts,
+                             float *weights, int64_t stream);
 /* Small batches: hidden[t][k][:] = act(gate_up[e][0:ff] x_t) * (gate_up[e][ff:2ff] x_t), e = experts[t][k]
  * (gate_up [n_experts, 2 * ff, width]), then out[t] = sum_k weights[t][k] * down[e] hidden[t][k]
  * (down [n_experts, width, ff]). */
@@ -202,6 +287,9 @@ int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype, const int
                         int ff, int act, void *hidden, int64_t stream);
 int mrs_seq_moe_down(const void *hidden, const void *down, int dtype, const int32_t *experts, const float *weights, int n_tok,
                      int top, int width, int ff, void *out, int64_t stream);
+/* mrs_seq_moe_gate_up with any joining rule */
+int mrs_seq_moe_gate_up_rule(const void *x, const void *gate_up, int dtype, const int32_t *experts, int n_tok, int top, int width,
+                             int ff, const mrs_seq_glu_rule *rule, void *hidden, int64_t stream);
 /* The plain rule: the `top` experts with the largest logits, weights = softmax over the chosen logits alone. */
 int mrs_seq_moe_route_top_softmax(const float *logits, int n_tok, int n_experts, int top, int32_t *experts, float *weights,
                                   int64_t stream);

@@ -1,5 +1,6 @@
-// moe.cu — mixture of experts: the routing rule (softmax scores, a choice bias that does not enter the weights,
-// selection limited to the best groups of neighbouring experts), the expert feed-forward for small batches as two
+// moe.cu — mixture of experts: the routing rule (softmax or sigmoid scores, a choice bias that does not enter the weights,
+// selection limited to the best groups of neighbouring experts, a group scored by its largest choice or by the sum of its
+// few largest), the expert feed-forward for small batches as two
 // weight-streaming kernels, and the sort / gather / combine steps around per-expert matrix products for large ones.
 #include "seq_common.cuh"
 
@@ -9,25 +10,30 @@ constexpr int ROUTE_MAX_EXPERTS = 1024;
 
 // one warp per token; scores and choices of all experts in shared memory
 __global__ void moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ correction, int n_tok, int n_experts,
-                                 int n_groups, int keep_groups, int top, int renorm, int32_t *__restrict__ experts,
-                                 float *__restrict__ weights) {
+                                 int n_groups, int keep_groups, int top, int renorm, int score_fn, int group_top, float weight_scale,
+                                 int32_t *__restrict__ experts, float *__restrict__ weights) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const int t = blockIdx.x * nw + wib;
   if (t >= n_tok) return;
   float *score = sm + (size_t)wib * (2 * n_experts + n_groups), *choice = score + n_experts, *gscore = choice + n_experts;
   const float *z = logits + (int64_t)t * n_experts;
-  float mx = -INFINITY;
-  for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float sum = 0.0f;
-  for (int e = lane; e < n_experts; e += 32) {
-    const float p = expf(z[e] - mx);
-    score[e] = p;
-    sum += p;
+  float inv = 1.0f;
+  if (score_fn == MRS_SEQ_SCORE_SIGMOID) {
+    for (int e = lane; e < n_experts; e += 32) score[e] = sigmoid_f(z[e]);
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float p = expf(z[e] - mx);
+      score[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    inv = 1.0f / sum;
   }
-  sum = warp_sum(sum);
-  const float inv = 1.0f / sum;
   for (int e = lane; e < n_experts; e += 32) {
     const float s = score[e] * inv;
     score[e] = s;
@@ -38,7 +44,25 @@ __global__ void moe_route_kernel(const float *__restrict__ logits, const float *
   if (keep_groups < n_groups) {
     for (int gi = lane; gi < n_groups; gi += 32) {
       float best = -INFINITY;
-      for (int e = gi * per; e < (gi + 1) * per; e++) best = fmaxf(best, choice[e]);
+      if (group_top <= 1) {
+        for (int e = gi * per; e < (gi + 1) * per; e++) best = fmaxf(best, choice[e]);
+      } else {      // the sum of the group's group_top largest choices: take them one by one, below the last one taken
+        float total = 0.0f, last = INFINITY;
+        int last_e = -1;
+        for (int r = 0; r < group_top && r < per; r++) {
+          float bv = -INFINITY;
+          int be = -1;
+          for (int e = gi * per; e < (gi + 1) * per; e++) {
+            const float v = choice[e];
+            if ((v < last || (v == last && e > last_e)) && (be < 0 || v > bv)) { bv = v; be = e; }
+          }
+          if (be < 0) break;
+          total += bv;
+          last = bv;
+          last_e = be;
+        }
+        best = total;
+      }
       gscore[gi] = best;
     }
     __syncwarp();
@@ -87,14 +111,16 @@ __global__ void moe_route_kernel(const float *__restrict__ logits, const float *
   }
   if (renorm && lane == 0 && wsum > 0.0f)
     for (int r = 0; r < top; r++) weights[(int64_t)t * top + r] /= wsum;
+  if (weight_scale != 1.0f && lane == 0)
+    for (int r = 0; r < top; r++) weights[(int64_t)t * top + r] *= weight_scale;
 }
 
 // hidden[t][k][r] = act(gate_up[e][r] . x_t) * (gate_up[e][ff + r] . x_t): one warp per output element;
 // blockIdx.y is the (token, k) pair, pairs laid out [token][k]
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T *__restrict__ x, const T *__restrict__ gate_up,
-                                                          const int32_t *__restrict__ experts, int top, int width, int ff, int act,
-                                                          T *__restrict__ hidden) {
+                                                          const int32_t *__restrict__ experts, int top, int width, int ff,
+                                                          const mrs_seq_glu_rule rule, T *__restrict__ hidden) {
   extern __shared__ __align__(16) float xs[];   // [width]
   const int pair = blockIdx.y, tok = pair / top;
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -109,7 +135,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T *__restrict__ 
     if (lane == 0) {
       // the products leave the "matrix product" in the activation type, as the large-batch path's do
       const float gt = to_f32<T>(from_f32<T>(ag)), up = to_f32<T>(from_f32<T>(au));
-      hidden[(int64_t)pair * ff + r] = from_f32<T>(apply_act(gt, act) * up);
+      hidden[(int64_t)pair * ff + r] = from_f32<T>(glu_join(gt, up, rule));
     }
   }
 }
@@ -243,14 +269,22 @@ using namespace seq;
 
 extern "C" int mrs_seq_moe_route(const float *logits, const float *correction, int n_tok, int n_experts, int n_groups, int keep_groups,
                                  int top, int renorm, int32_t *experts, float *weights, int64_t stream) {
+  return mrs_seq_moe_route_scored(logits, correction, n_tok, n_experts, n_groups, keep_groups, top, renorm, MRS_SEQ_SCORE_SOFTMAX, 1, 1.0f,
+                                  experts, weights, stream);
+}
+
+extern "C" int mrs_seq_moe_route_scored(const float *logits, const float *correction, int n_tok, int n_experts, int n_groups, int keep_groups,
+                                        int top, int renorm, int score_fn, int group_top, float weight_scale, int32_t *experts,
+                                        float *weights, int64_t stream) {
   if (n_tok <= 0) return 0;
   if (n_experts < 1 || n_experts > ROUTE_MAX_EXPERTS || n_groups < 1 || n_experts % n_groups || keep_groups < 1 ||
-      keep_groups > n_groups || top < 1 || top > n_experts)
+      keep_groups > n_groups || top < 1 || top > n_experts || group_top < 1 ||
+      (score_fn != MRS_SEQ_SCORE_SOFTMAX && score_fn != MRS_SEQ_SCORE_SIGMOID))
     return -2;
   const int warps = 4;
   const size_t bytes = (size_t)warps * (2 * n_experts + n_groups) * sizeof(float);
   moe_route_kernel<<<(n_tok + warps - 1) / warps, warps * 32, bytes, (cudaStream_t)stream>>>(
-      logits, correction, n_tok, n_experts, n_groups, keep_groups, top, renorm, experts, weights);
+      logits, correction, n_tok, n_experts, n_groups, keep_groups, top, renorm, score_fn, group_top, weight_scale, experts, weights);
   return launch_status();
 }
 
@@ -285,7 +319,14 @@ extern "C" int mrs_seq_moe_up(const void *x, const void *up, int dtype, const in
 
 extern "C" int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype, const int32_t *experts, int n_tok, int top, int width,
                                    int ff, int act, void *hidden, int64_t stream) {
+  const mrs_seq_glu_rule rule = {act, 0.0f, 0.0f, 0.0f};
+  return mrs_seq_moe_gate_up_rule(x, gate_up, dtype, experts, n_tok, top, width, ff, &rule, hidden, stream);
+}
+
+extern "C" int mrs_seq_moe_gate_up_rule(const void *x, const void *gate_up, int dtype, const int32_t *experts, int n_tok, int top, int width,
+                                        int ff, const mrs_seq_glu_rule *rule, void *hidden, int64_t stream) {
   if (n_tok <= 0) return 0;
+  if (!rule) return -2;
   if ((size_t)width * sizeof(float) > 160 * 1024) return -2;
   const int warps = 8, bx = (ff + warps - 1) / warps;
   const size_t bytes = (size_t)width * sizeof(float);
@@ -297,7 +338,7 @@ extern "C" int mrs_seq_moe_gate_up(const void *x, const void *gate_up, int dtype
       allowed = bytes;
     }
     kern<<<dim3(bx < 256 ? bx : 256, n_tok * top), warps * 32, bytes, (cudaStream_t)stream>>>(
-        (const T *)x, (const T *)gate_up, experts, top, width, ff, act, (T *)hidden);
+        (const T *)x, (const T *)gate_up, experts, top, width, ff, *rule, (T *)hidden);
   });
   return launch_status();
 }

@@ -4,8 +4,10 @@
 //
 //   S_t = a_t S_(t-1) + b_t k_t v_t^T ,  o_t = S_t^T q_t + skip v_t
 //
-// covers linear attention with a fixed per-head decay (a_t constant, b_t = 1, silu on q / k / v) and the state-space
-// form (k = B, q = C, v = x, a_t = exp(-exp(A_log) dt_t), b_t = dt_t, skip = D).  The same kernel runs a prompt
+// covers linear attention with a fixed per-head decay (a_t constant, b_t = 1, silu on q / k / v), the state-space
+// form (k = B, q = C, v = x, a_t = exp(-exp(A_log) dt_t), b_t = dt_t, skip = D) and — template flag VD — a forget gate
+// per state ROW that also decides what is written (S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T: the key is the gate's
+// complement and is formed here, in f32, from the same staged row).  The same kernel runs a prompt
 // portion and a single decoded token: the state is read from the sequence's slot (or taken as zero when the
 // sequence starts), advanced token by token in registers, and written back.
 #include "seq_common.cuh"
@@ -44,8 +46,8 @@ __device__ __forceinline__ void cp_async4(void *dst, const void *src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-template <typename T, int RK, int TC>
-__global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned, int mode) {
+template <typename T, int RK, int TC, bool VD>
+__global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_kernel(const mrs_seq_scan_args a, int parts, int cw, int aligned, int mode) {
   // mode 0: the whole portion of a sequence, state from / to its slot.  Long portions are cut into segments of
   // a.seg_len tokens that run side by side: mode 1 advances a ZERO state over one segment and leaves it, with the
   // segment's product of decays, in a.seg_state / a.seg_decay; a small kernel then chains the segments (and the slot's
@@ -68,7 +70,8 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
   const int dkr = (dk + N - 1) / N * N, cwr = (cw + N - 1) / N * N;      // raw row lengths (elements), 16-byte multiples
   float *qs = smem, *ks = qs + TC * dks, *vs = ks + TC * dks, *os = vs + TC * cw, *as = os + TC * cw, *bs = as + TC;
   float *ra = bs + TC, *rb = ra + TC;
-  T *rq = (T *)(rb + TC), *rk = rq + TC * dkr, *rv = rk + TC * dkr;
+  float *ds = rb + TC, *rd = ds + (VD ? TC * dks : 0);      // per-row decays: working set (laid out like ks) and raw staging
+  T *rq = (T *)(rd + (VD ? TC * dkr : 0)), *rk = rq + TC * dkr, *rv = rk + TC * dkr;
   float *state = mode ? a.seg_state + ((int64_t)blockIdx.z * heads + h) * dk * dv : a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
   float decay_product = 1.0f;
 
@@ -99,8 +102,12 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
     for (int r = 0; r < RK / 2; r++) S[r] = 0ull;
   }
   for (int e = threadIdx.x; e < 2 * TC * dks; e += nth) qs[e] = 0.0f;     // rows past dk stay zero for good
+  if (VD)
+    for (int e = threadIdx.x; e < TC * dks; e += nth) ds[e] = 0.0f;
   const float skip = a.skip ? a.skip[h] : 0.0f;
-  const T *q = (const T *)a.q + g * dk, *k = (const T *)a.k + g * dk, *v = (const T *)a.v + h * dv + col0;
+  const T *q = (const T *)a.q + g * dk, *k = VD ? nullptr : (const T *)a.k + g * dk, *v = (const T *)a.v + h * dv + col0;
+  const float *dvec = VD ? a.decay_vec + (int64_t)h * dk : nullptr;
+  const bool dvec_aligned = VD && dk % 4 == 0 && ((uintptr_t)a.decay_vec & 15) == 0;
   const int vcols = min(cw, dv - col0);
 
   auto issue = [&](int c0) {      // round starting at token c0 -> raw staging
@@ -110,7 +117,7 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
       for (int e = threadIdx.x; e < n * per; e += nth) {
         const int i = e / per, j = e % per;
         cp_async16(rq + i * dkr + j * N, q + (int64_t)(c0 + i) * a.q_ld + j * N);
-        cp_async16(rk + i * dkr + j * N, k + (int64_t)(c0 + i) * a.k_ld + j * N);
+        if (!VD) cp_async16(rk + i * dkr + j * N, k + (int64_t)(c0 + i) * a.k_ld + j * N);
       }
       const int perv = vcols / N;
       for (int e = threadIdx.x; e < n * perv; e += nth) {
@@ -121,11 +128,25 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
       for (int e = threadIdx.x; e < n * dk; e += nth) {
         const int i = e / dk, d = e % dk;
         rq[i * dkr + d] = q[(int64_t)(c0 + i) * a.q_ld + d];
-        rk[i * dkr + d] = k[(int64_t)(c0 + i) * a.k_ld + d];
+        if (!VD) rk[i * dkr + d] = k[(int64_t)(c0 + i) * a.k_ld + d];
       }
       for (int e = threadIdx.x; e < n * vcols; e += nth) {
         const int i = e / vcols, c = e % vcols;
         rv[i * cwr + c] = v[(int64_t)(c0 + i) * a.v_ld + c];
+      }
+    }
+    if (VD) {
+      if (dvec_aligned) {
+        const int per = dk / 4;
+        for (int e = threadIdx.x; e < n * per; e += nth) {
+          const int i = e / per, j = e % per;
+          cp_async16(rd + i * dkr + j * 4, dvec + (int64_t)(c0 + i) * heads * dk + j * 4);
+        }
+      } else {
+        for (int e = threadIdx.x; e < n * dk; e += nth) {
+          const int i = e / dk, d = e % dk;
+          rd[i * dkr + d] = dvec[(int64_t)(c0 + i) * heads * dk + d];
+        }
       }
     }
     if (threadIdx.x < n) {
@@ -150,7 +171,13 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
         for (int x = 0; x < N; x++) {
           const bool in = d0 + x < dk;
           qs[at + x] = in ? apply_act(to_f32<T>(rq[i * dkr + d0 + x]), a.act) : 0.0f;
-          ks[at + x] = in ? apply_act(to_f32<T>(rk[i * dkr + d0 + x]), a.act) : 0.0f;
+          if (VD) {
+            const float f = in ? rd[i * dkr + d0 + x] : 0.0f;
+            ds[at + x] = f;
+            ks[at + x] = in ? 1.0f - f : 0.0f;
+          } else {
+            ks[at + x] = in ? apply_act(to_f32<T>(rk[i * dkr + d0 + x]), a.act) : 0.0f;
+          }
         }
       }
       for (int e = threadIdx.x; e < n * cw; e += nth) {
@@ -158,7 +185,7 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
         vs[e] = c < vcols ? apply_act(to_f32<T>(rv[i * cwr + c]), a.act) : 0.0f;
       }
       if (threadIdx.x < n) {
-        as[threadIdx.x] = a.decay_tok ? ra[threadIdx.x] : a.decay_head[h];
+        as[threadIdx.x] = VD ? 1.0f : (a.decay_tok ? ra[threadIdx.x] : a.decay_head[h]);
         bs[threadIdx.x] = a.scale_tok ? rb[threadIdx.x] : 1.0f;
       }
     }
@@ -169,9 +196,11 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
     for (int i0 = 0; i0 < n; i0 += 4) {
       float vv[4];
       uint64_t av2[4], bv2[4], acc2[4];
+      bool lv[4];
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        const bool live = i0 + u < n;          // a missing token leaves the state alone (rows past n hold old, finite data)
+        const bool live = i0 + u < n;
+        lv[u] = live;          // a missing token leaves the state alone (rows past n hold old, finite data)
         vv[u] = vs[(i0 + u) * cw + cl];
         const float av = live ? as[i0 + u] : 1.0f, bv = live ? bs[i0 + u] * vv[u] : 0.0f;
         av2[u] = pack2(av, av);
@@ -190,8 +219,14 @@ __global__ void __launch_bounds__(256, RK <= 16 ? 3 : 1) linear_scan_kernel(cons
         uint64_t s01 = S[r / 2], s23 = S[r / 2 + 1];
 #pragma unroll
         for (int u = 0; u < 4; u++) {
-          s01 = fma2(k4[u].x, bv2[u], mul2(av2[u], s01));
-          s23 = fma2(k4[u].y, bv2[u], mul2(av2[u], s23));
+          if (VD) {      // this row's own decay; a missing token keeps the state as it is
+            const ulonglong2 d4 = *(const ulonglong2 *)(ds + (i0 + u) * dks + part * PS + r);
+            s01 = fma2(k4[u].x, bv2[u], mul2(lv[u] ? d4.x : av2[u], s01));
+            s23 = fma2(k4[u].y, bv2[u], mul2(lv[u] ? d4.y : av2[u], s23));
+          } else {
+            s01 = fma2(k4[u].x, bv2[u], mul2(av2[u], s01));
+            s23 = fma2(k4[u].y, bv2[u], mul2(av2[u], s23));
+          }
           if (mode != 1) acc2[u] = fma2(s01, q4[u].x, fma2(s23, q4[u].y, acc2[u]));
         }
         S[r / 2] = s01;
@@ -261,7 +296,7 @@ __global__ void scan_chain_kernel(const mrs_seq_scan_args a) {
   *slot_state = run;
 }
 
-template <typename T, int RK, int TC>
+template <typename T, int RK, int TC, bool VD>
 static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
   constexpr int N = 16 / (int)sizeof(T);
   int parts = 1;
@@ -273,19 +308,20 @@ static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
   while (cw / 2 >= unit && (cw / 2) % unit == 0 && (cw / 2) * parts >= 64 && (int64_t)((a.dv + cw - 1) / cw) * a.heads * a.n_seq * (a.n_segs > 1 ? a.n_segs : 1) < 148) cw /= 2;   // fill the SMs
   if (cw * parts > 256 || (cw * parts) % 32) return -2;
   const int dks = parts * (RK + 4), dkr = (a.dk + N - 1) / N * N, cwr = (cw + N - 1) / N * N;
-  const size_t work = (size_t)(2 * TC * dks + 2 * TC * cw + 4 * TC) * sizeof(float) + (size_t)(2 * TC * dkr + TC * cwr) * sizeof(T);
+  const size_t work = (size_t)(2 * TC * dks + 2 * TC * cw + 4 * TC + (VD ? TC * dks + TC * dkr : 0)) * sizeof(float) +
+                      (size_t)(2 * TC * dkr + TC * cwr) * sizeof(T);
   const size_t tile = (size_t)parts * RK * cw * sizeof(float);
   const size_t bytes = work > tile ? work : tile;
-  const bool aligned = a.dk % N == 0 && a.dv % N == 0 && cw % N == 0 && a.q_ld % N == 0 && a.k_ld % N == 0 && a.v_ld % N == 0 &&
-                       (uintptr_t)a.q % 16 == 0 && (uintptr_t)a.k % 16 == 0 && (uintptr_t)a.v % 16 == 0;
-  auto kern = linear_scan_kernel<T, RK, TC>;
+  const bool aligned = a.dk % N == 0 && a.dv % N == 0 && cw % N == 0 && a.q_ld % N == 0 && (VD || a.k_ld % N == 0) && a.v_ld % N == 0 &&
+                       (uintptr_t)a.q % 16 == 0 && (VD || (uintptr_t)a.k % 16 == 0) && (uintptr_t)a.v % 16 == 0;
+  auto kern = linear_scan_kernel<T, RK, TC, VD>;
   static size_t allowed = 48 * 1024;      // per instantiation; raised once per size, so a captured step repeats no attribute call
   if (bytes > allowed) {
     const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return (int)e;
     allowed = bytes;
   }
-  if (a.n_segs > 1 && a.seg_state && a.seg_decay && a.seg_len > 0) {
+  if (!VD && a.n_segs > 1 && a.seg_state && a.seg_decay && a.seg_len > 0) {   // per-row decays run every portion in one pass
     dim3 grid((a.dv + cw - 1) / cw, a.heads, a.n_seq * a.n_segs);
     kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0, 1);
     const int per = a.dk * a.dv;
@@ -421,17 +457,17 @@ __global__ void activate_cols_kernel(T *__restrict__ x, int64_t ld, int cols, in
 }
 
 template <typename T>
-__global__ void glu_split_kernel(const T *__restrict__ x, T *__restrict__ out, int half, int act, int vec) {
+__global__ void glu_split_kernel(const T *__restrict__ x, T *__restrict__ out, int half, const mrs_seq_glu_rule rule, int vec) {
   const T *row = x + (int64_t)blockIdx.x * 2 * half;
   T *dst = out + (int64_t)blockIdx.x * half;
   if (vec) {
     for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < half; c += gridDim.y * blockDim.x * 4) {
-      const float4 g = act4(load4<T>(row + c), act), u = load4<T>(row + half + c);
-      store4<T>(dst + c, make_float4(g.x * u.x, g.y * u.y, g.z * u.z, g.w * u.w));
+      const float4 g = load4<T>(row + c), u = load4<T>(row + half + c);
+      store4<T>(dst + c, make_float4(glu_join(g.x, u.x, rule), glu_join(g.y, u.y, rule), glu_join(g.z, u.z, rule), glu_join(g.w, u.w, rule)));
     }
   } else {
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < half; c += gridDim.y * blockDim.x)
-      dst[c] = from_f32<T>(apply_act(to_f32<T>(row[c]), act) * to_f32<T>(row[half + c]));
+      dst[c] = from_f32<T>(glu_join(to_f32<T>(row[c]), to_f32<T>(row[half + c]), rule));
   }
 }
 
@@ -443,11 +479,18 @@ extern "C" int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream
   const mrs_seq_scan_args &a = *args;
   if (a.n_tok <= 0 || a.n_seq <= 0) return 0;
   if (a.heads <= 0 || a.qk_groups <= 0 || a.heads % a.qk_groups || a.dk <= 0 || a.dv <= 0) return -2;
-  if (!a.decay_tok && !a.decay_head) return -2;
+  if (!a.decay_tok && !a.decay_head && !a.decay_vec) return -2;
+  if (a.decay_vec ? (a.decay_tok || a.decay_head || a.qk_groups != a.heads) : !a.k) return -2;
   cudaStream_t st = (cudaStream_t)stream;
-  if (a.dk <= 128) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 16, 16>(a, st)));
-  if (a.dk <= 512) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 32, 8>(a, st)));
-  if (a.dk <= 2048) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 64, 4>(a, st)));
+  if (a.decay_vec) {
+    if (a.dk <= 128) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 16, 16, true>(a, st)));
+    if (a.dk <= 512) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 32, 8, true>(a, st)));
+    if (a.dk <= 2048) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 64, 4, true>(a, st)));
+    return -2;
+  }
+  if (a.dk <= 128) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 16, 16, false>(a, st)));
+  if (a.dk <= 512) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 32, 8, false>(a, st)));
+  if (a.dk <= 2048) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 64, 4, false>(a, st)));
   return -2;
 }
 
@@ -503,12 +546,38 @@ extern "C" int mrs_seq_gated_group_norm(const float *x, const void *gate, int64_
   return launch_status();
 }
 
-extern "C" int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream) {
+extern "C" int mrs_seq_glu_join(const void *x, void *out, int dtype, int n_tok, int half, const mrs_seq_glu_rule *rule, int64_t stream) {
   if (n_tok <= 0 || half <= 0) return 0;
+  if (!rule) return -2;
   const int vec = half % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0;
   const int per = vec ? 1024 : 256, by = (half + per - 1) / per;
   SEQ_DISPATCH_DTYPE(dtype, (glu_split_kernel<T><<<dim3(n_tok, by < 64 ? by : 64), 256, 0, (cudaStream_t)stream>>>(
-                                (const T *)x, (T *)out, half, act, vec)));
+                                (const T *)x, (T *)out, half, *rule, vec)));
+  return launch_status();
+}
+
+extern "C" int mrs_seq_glu_split(const void *x, void *out, int dtype, int n_tok, int half, int act, int64_t stream) {
+  const mrs_seq_glu_rule rule = {act, 0.0f, 0.0f, 0.0f};
+  return mrs_seq_glu_join(x, out, dtype, n_tok, half, &rule, stream);
+}
+
+// gate = lower + (1 - lower) * sigmoid(raw + bias), f32
+template <typename T>
+__global__ void bounded_gate_kernel(const T *__restrict__ raw, int64_t raw_ld, const float *__restrict__ bias, const float *__restrict__ lower,
+                                    int cols, float *__restrict__ gate) {
+  const int t = blockIdx.x;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += gridDim.y * blockDim.x) {
+    const float lo = lower ? lower[c] : 0.0f;
+    gate[(int64_t)t * cols + c] = lo + (1.0f - lo) * seq::sigmoid_f(seq::to_f32<T>(raw[(int64_t)t * raw_ld + c]) + (bias ? bias[c] : 0.0f));
+  }
+}
+
+extern "C" int mrs_seq_bounded_gate(const void *raw, int64_t raw_ld, int dtype, const float *bias, const float *lower, int n_tok, int cols,
+                                    float *gate, int64_t stream) {
+  if (n_tok <= 0 || cols <= 0) return 0;
+  const int by = (cols + 255) / 256;
+  SEQ_DISPATCH_DTYPE(dtype, (bounded_gate_kernel<T><<<dim3(n_tok, by < 64 ? by : 64), 256, 0, (cudaStream_t)stream>>>(
+                                (const T *)raw, raw_ld, bias, lower, cols, gate)));
   return launch_status();
 }
 

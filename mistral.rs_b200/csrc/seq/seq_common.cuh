@@ -40,6 +40,16 @@ __device__ __forceinline__ float apply_act(float z, int act) {
   }
 }
 
+// gate and up halves of a gated feed-forward joined by a rule (mrs_seq_glu_rule)
+__device__ __forceinline__ float glu_join(float g, float u, const mrs_seq_glu_rule &r) {
+  if (r.act == MRS_SEQ_GLU_CAPPED) {
+    g = fminf(g, r.limit);
+    u = fminf(fmaxf(u, -r.limit), r.limit);
+    return g * sigmoid_f(r.slope * g) * (u + r.shift);
+  }
+  return apply_act(g, r.act) * u;
+}
+
 // ---- reductions -------------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll

@@ -105,7 +105,8 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
                                                                const int32_t *__restrict__ pages,
                                                                int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
                                                                const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index,
-                                                               int n_tok, T *__restrict__ out, int64_t out_ld, float out_scale) {
+                                                               int n_tok, T *__restrict__ out, int64_t out_ld, float out_scale, int64_t k_row,
+                                                               int64_t v_row) {
   extern __shared__ __align__(16) float qsm[];   // [warps][dk]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t job = (int64_t)blockIdx.x * (blockDim.x >> 5) + wib;
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
     int64_t slot = 0;
     if (j < jend) {
       slot = (int64_t)table[j / page_size] * page_size + j % page_size;
-      const T *kr = k_cache + (slot * kv_heads + g) * dk;
+      const T *kr = k_cache + slot * k_row + g * dk;
       float a0 = 0.0f, a1 = 0.0f;
       int d = 0;
       for (; d + 1 < dk; d += 2) {
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
     for (int i = 0; i < n; i++) {
       const float pi = __shfl_sync(0xffffffffu, p, i);
       const int64_t si = __shfl_sync(0xffffffffu, slot, i);
-      const T *vr = v_cache + (si * kv_heads + g) * dv;
+      const T *vr = v_cache + si * v_row + g * dv;
 #pragma unroll
       for (int c = 0; c < MAX_VCOLS; c++)
         if (c * 32 + lane < dv) acc[c] = fmaf(pi, to_f32<T>(vr[c * 32 + lane]), acc[c]);
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache, const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
     float scale, int window, int keep_first, const float *__restrict__ sink, const int32_t *__restrict__ pages, int pages_ld, int page_size,
     const int32_t *__restrict__ seq_of_tok, const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index, T *__restrict__ out,
-    int64_t out_ld, float out_scale) {
+    int64_t out_ld, float out_scale, int64_t k_row, int64_t v_row) {
   extern __shared__ __align__(16) float sm[];   // q [dk] | per warp: m, l, acc [VPAIRS * 64]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int ti = blockIdx.x / heads, h = blockIdx.x % heads, t = tok_index ? tok_index[ti] : ti, g = h / (heads / kv_heads);
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     int64_t slot = 0;
     if (j < jend) {
       slot = (int64_t)table[j / page_size] * page_size + j % page_size;
-      const T *kr = k_cache + (slot * kv_heads + g) * dk;
+      const T *kr = k_cache + slot * k_row + g * dk;
       float a0 = 0.0f, a1 = 0.0f;
       int d = 0;
 #pragma unroll 4
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
         const float pu = __shfl_sync(0xffffffffu, p, i);
         pi[u] = i0 + u < n ? pu : 0.0f;
         const int64_t si = __shfl_sync(0xffffffffu, slot, i);
-        const T *vr = v_cache + (si * kv_heads + g) * dv;          // a lane past n carries slot 0: a valid row, weight 0
+        const T *vr = v_cache + si * v_row + g * dv;               // a lane past n carries slot 0: a valid row, weight 0
 #pragma unroll
         for (int c = 0; c < VPAIRS; c++)
           vv[u][c] = c * 64 + 2 * lane < dv ? load2<T>(vr + c * 64 + 2 * lane) : make_float2(0.0f, 0.0f);
@@ -316,13 +317,15 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
   const int keep_first = a.keep_first > 0 ? a.keep_first : 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
-  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 256 && ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 8) == 0;
+  const int64_t k_row = a.k_row > 0 ? a.k_row : (int64_t)kv_heads * dk, v_row = a.v_row > 0 ? a.v_row : (int64_t)kv_heads * dv;
+  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 256 && ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 8) == 0 &&
+                   k_row % (16 / elem) == 0 && v_row % 2 == 0;
   if (vec) {
     constexpr int SPLIT = 8;
 #define SEQ_ATTN_VEC(VP)                                                                                                         \
   window_attention_vec_kernel<T, VP, SPLIT><<<(unsigned)n_tok * heads, SPLIT * 32, (dk + SPLIT * (2 + VP * 64)) * sizeof(float), st>>>( \
       (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink,  \
-      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, (T *)a.out, a.out_ld, a.out_scale)
+      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row)
     SEQ_DISPATCH_DTYPE(dtype, {
       if (dv <= 64) SEQ_ATTN_VEC(1);
       else if (dv <= 128) SEQ_ATTN_VEC(2);
@@ -336,7 +339,7 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
 #define SEQ_ATTN_LAUNCH(VC)                                                                                              \
   window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float), st>>>(  \
       (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink, \
-      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, n_tok, (T *)a.out, a.out_ld, a.out_scale)
+      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, n_tok, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row)
   SEQ_DISPATCH_DTYPE(dtype, {
     if (dv <= 64) SEQ_ATTN_LAUNCH(2);
     else if (dv <= 128) SEQ_ATTN_LAUNCH(4);

@@ -2,8 +2,10 @@
 model definition can compose them: multi-stream residuals, Dynamic Tanh norms around a single residual, linear
 attention with per-head decay, a stabilised matrix memory (mLSTM), softmax attention over a paged cache (query/key
 norm per head or over the whole projection, rotary positions with scaled frequencies, window with kept first tokens,
-sink, values that are the keys), a Mamba-2 style state-space mixer, two mixers side by side, dense GLU / plain and
-routed-expert feed-forwards.
+sink, values that are the keys), attention through a shared low-rank latent (one cached latent per token, which a later
+layer may reuse), a linear recurrence whose per-channel forget gate also writes (HGRN2), a short causal convolution added
+to a sublayer's input, a Mamba-2 style state-space mixer, two mixers side by side, dense GLU / plain and routed-expert
+feed-forwards (softmax or sigmoid routing, groups scored by their best or their few best experts, plain or capped GLU).
 
 A mechanism owns its device weights and declares the per-layer cache it needs (`alloc_cache`): token-indexed pages
 (sized by the engine's block pool) and / or per-request state slots (sized by the engine's slot pool).  `forward`
@@ -57,7 +59,8 @@ class TanhNorm:
 
 
 class Rotation:
-    """Rotary positions on the first `dims` entries of every head, pairs (i, i + dims / 2), frequency base^(-2i/dims).
+    """Rotary positions on the first `dims` entries of every head, frequency base^(-2i/dims) for pair i.  Which two entries
+    make pair i, (i, i + dims / 2) or the neighbours (2i, 2i + 1), is the choice of the kernel that applies the table.
     `scaling` (YaRN: factor, original, fast, slow) divides the slow frequencies by `factor` along a linear ramp between
     the pair indices at which `original` positions make `fast` and `slow` turns, and multiplies cos and sin by
     0.1 ln(factor) + 1.  Frequencies are formed in double on the host; the table of a step (one per distinct
@@ -144,6 +147,94 @@ class WindowAttention:
                 return
         K.paged_attention(y, col0, cache["k"], cache["v"], self.heads, self.kv_heads, self.dk, self.dv, self.scale, self.window,
                           self.keep_first, self.sink, batch, page_size, out, out_col, out_scale, tok_index)
+
+
+class InputConvolution:
+    """h <- h + conv(h): a causal convolution over time on every channel, conv(h)_t = sum_j taps[:, j] h_(t - n + 1 + j), added
+    to its own input before a sublayer reads it.  The last n - 1 inputs of every request are state (one slot each); the
+    identity rides on the last tap, so this is the package's short-convolution kernel with f32 taps."""
+
+    def __init__(self, taps):
+        w = taps.to(torch.float32).clone()
+        w[:, -1] += 1.0
+        self.taps = w.contiguous()
+
+    def alloc_cache(self, n_slots, device):
+        return torch.zeros(n_slots, max(self.taps.shape[1] - 1, 1), self.taps.shape[0], dtype=torch.float32, device=device)
+
+    def forward(self, h, batch, state):
+        return K.causal_conv(h, 0, self.taps.shape[0], self.taps, None, K.ACT_NONE, state, batch)
+
+
+class LatentAttentionMixer:
+    """Multi-head latent attention.  Queries: c_q = rms_norm(W_dq h) w, q = W_uq c_q, per head [dn plain | dr rotated].
+    Keys / values: W_dkv h = [kv_rank | dr]; c = rms_norm(first part) w is the latent, the last dr entries (rotated, not
+    normed) are one key part all heads share; k_h = [W_uk,h c | shared part], v_h = W_uv,h c.  Only c and the shared part
+    are cached (one row of kv_rank + dr per token).  Rotation turns neighbouring pairs.  Scores are scaled by a given
+    constant; position i sees j with 0 <= i - j < window (0: all).
+
+    Computed in the absorbed form: a head's query becomes [W_uk,h^T q_plain | q_rot] (size kv_rank + dr), attention runs
+    over the cached rows as one key/value head whose values are the rows' first kv_rank columns, and W_uv,h maps the
+    result to the head's output.  `shares`: this mixer has no W_dkv and reads the cache another layer fills."""
+
+    def __init__(self, w_down, w_uq, w_uk, w_uv, w_o, q_norm_w, kv_norm_w, heads, dn, dr, dv, q_rank, kv_rank, scale, window, rotation, eps,
+                 page_size, shares=False):
+        self.w_down, self.w_uq, self.w_o, self.q_norm_w, self.kv_norm_w = w_down, w_uq, w_o, q_norm_w, kv_norm_w
+        self.w_uk = w_uk.view(heads, dn, kv_rank)                       # [H][dn][r]: q_plain,h @ w_uk[h] = W_uk,h^T q_plain,h
+        self.w_uv_t = w_uv.view(heads, dv, kv_rank).transpose(1, 2)     # [H][r][dv]
+        self.heads, self.dn, self.dr, self.dv, self.q_rank, self.kv_rank = heads, dn, dr, dv, q_rank, kv_rank
+        self.scale, self.window, self.rotation, self.eps, self.page_size, self.shares = scale, window, rotation, eps, page_size, shares
+        self.row = kv_rank + dr
+
+    def alloc_cache(self, n_slots, n_token_slots, dtype, device):
+        if self.shares:
+            return {}
+        row = -(-self.row // 8) * 8            # rows start on 16-byte boundaries
+        return {"latent": torch.zeros(n_token_slots, row, dtype=dtype, device=device)}
+
+    def forward(self, h, batch, cache):
+        T, H, dn, dr, R = h.shape[0], self.heads, self.dn, self.dr, self.kv_rank
+        latent = cache["latent"]
+        cos_sin = self.rotation.table(batch) if self.rotation is not None else None
+        rot_dims = self.rotation.dims if self.rotation is not None else 0
+        y = linear(h, self.w_down)                                           # query latent | (key/value latent | shared key part)
+        cq = torch.empty(T, self.q_rank, dtype=h.dtype, device=h.device)
+        K.latent_prepare(y, 0, self.q_rank, self.q_norm_w, cq, self.q_rank, 0 if self.shares else R, dr, rot_dims, self.kv_norm_w, cos_sin,
+                         self.eps, latent, batch.slot_of_tok)
+        q = linear(cq, self.w_uq).view(T, H, dn + dr)
+        qa = torch.empty(T, H, self.row, dtype=h.dtype, device=h.device)      # the absorbed queries
+        torch.bmm(q[:, :, :dn].transpose(0, 1), self.w_uk, out=qa[:, :, :R].transpose(0, 1))
+        K.rotate_pairs(q.view(T, -1), dn, dn + dr, qa.view(T, -1), R, self.row, H, dr, rot_dims, cos_sin)
+        o = torch.empty(T, H, R, dtype=h.dtype, device=h.device)
+        K.latent_attention(qa.view(T, -1), latent, H, R, dr, self.scale, self.window, batch, self.page_size, o.view(T, -1))
+        out = torch.empty(T, H, self.dv, dtype=h.dtype, device=h.device)
+        torch.bmm(o.transpose(0, 1), self.w_uv_t, out=out.transpose(0, 1))
+        return linear(out.view(T, H * self.dv), self.w_o)
+
+
+class TiedGateMixer:
+    """HGRN2: linear attention whose forget gate also decides what is written.  q = silu(W_q h), v = W_v h, per head and
+    channel f = lower + (1 - lower) sigmoid(W_f h + b) in f32; S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t;
+    every head's o is RMS-normed over its value size with weights shared by the heads; output projection.  The
+    recurrence is the package's linear scan with a decay per state row, whose key is the decay's complement."""
+
+    def __init__(self, w_qfv, f_bias, lower, w_o, norm_w, heads, dk, dv, eps):
+        self.w_qfv, self.f_bias, self.lower, self.w_o = w_qfv, f_bias, lower, w_o
+        self.norm_w = norm_w.repeat(heads).contiguous()            # the group norm takes one weight per column
+        self.heads, self.dk, self.dv, self.eps = heads, dk, dv, eps
+
+    def alloc_cache(self, n_slots, n_token_slots, dtype, device):
+        return {"state": torch.zeros(n_slots, self.heads, self.dk, self.dv, dtype=torch.float32, device=device)}
+
+    def forward(self, h, batch, cache):
+        H, dk, dv = self.heads, self.dk, self.dv
+        y = linear(h, self.w_qfv)                                          # [T, 2 H dk + H dv]: q | f | v
+        K.activate_cols(y, 0, H * dk, K.ACT_SILU)
+        f = K.bounded_gate(y, H * dk, H * dk, self.f_bias, self.lower)
+        o = K.linear_scan(y, 0, None, 0, y, 2 * H * dk, H, H, dk, dv, cache["state"], batch, decay_vec=f)
+        on = torch.empty(h.shape[0], H * dv, dtype=h.dtype, device=h.device)
+        K.gated_group_norm(o, None, 0, self.norm_w, H, self.eps, K.ACT_NONE, False, on)
+        return linear(on, self.w_o)
 
 
 class AttentionMixer:
@@ -274,8 +365,10 @@ class DenseMLP:
 
 class RoutedExperts:
     """Router logits in f32.  Rule "grouped_softmax": softmax over all experts, a choice-only bias, group-limited top-k,
-    weights = the scores (optionally renormalised).  Rule "top_softmax": the largest logits, weights = softmax over the
-    chosen logits alone.  Experts are GLU feed-forwards (`gated`: w_up holds gate | up rows) or plain down(act(up h)); a
+    weights = the scores (optionally renormalised).  Rule "grouped_sigmoid": the same with scores = sigmoid(logit).  In both
+    a group's score is the sum of its `group_top` largest choices and the weights are multiplied by `weight_scale`.  Rule
+    "top_softmax": the largest logits, weights = softmax over the chosen logits alone.  `act`: an activation code or a
+    `seq_ops.GluRule` (how gate and up are joined).  Experts are GLU feed-forwards (`gated`: w_up holds gate | up rows) or plain down(act(up h)); a
     `shared` feed-forward, when given, runs for every token and is added.  Few (token, expert) pairs: two
     weight-streaming kernels.  Many: rows sorted by expert, one GEMM pair per expert that has rows (the per-expert row
     counts cross to the host once per layer), weighted combine in f32."""
@@ -285,9 +378,10 @@ class RoutedExperts:
     SMALL_EXPERT_BYTES = 32 << 20
 
     def __init__(self, w_router, correction, w_gate_up, w_down, top, n_groups, keep_groups, act, renorm=False, rule="grouped_softmax",
-                 gated=True, shared=None):
-        if rule not in ("grouped_softmax", "top_softmax"):
+                 gated=True, shared=None, group_top=1, weight_scale=1.0):
+        if rule not in ("grouped_softmax", "grouped_sigmoid", "top_softmax"):
             raise ValueError(f"unknown routing rule {rule!r}")
+        self.group_top, self.weight_scale = int(group_top), float(weight_scale)
         self.w_router, self.correction, self.w_gate_up, self.w_down = w_router, correction, w_gate_up, w_down
         self.top, self.n_groups, self.keep_groups, self.act, self.renorm = top, n_groups, keep_groups, act, renorm
         self.rule, self.gated, self.shared = rule, gated, shared
@@ -302,7 +396,11 @@ class RoutedExperts:
         logits = F.linear(h.float(), self.w_router)
         if self.rule == "top_softmax":
             return K.moe_route_top_softmax(logits, self.top)
-        return K.moe_route(logits, self.correction, self.n_groups, self.keep_groups, self.top, self.renorm)
+        if self.rule == "grouped_softmax" and self.group_top == 1 and self.weight_scale == 1.0:
+            return K.moe_route(logits, self.correction, self.n_groups, self.keep_groups, self.top, self.renorm)
+        fn = K.SCORE_SIGMOID if self.rule == "grouped_sigmoid" else K.SCORE_SOFTMAX
+        return K.moe_route_scored(logits, self.correction, self.n_groups, self.keep_groups, self.top, self.renorm, fn, self.group_top,
+                                  self.weight_scale)
 
     def forward(self, h):
         experts, weights = self.route(h)

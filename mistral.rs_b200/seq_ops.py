@@ -13,6 +13,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SEQ_LIB_PATH = os.path.join(_HERE, "libmrs_b200_seq.so")
 BF16, F32 = 1, 2
 ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID, ACT_GELU_ERF, ACT_RELU_SQ = 0, 1, 2, 3, 4, 5
+GLU_CAPPED = 100
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 QK_NORM_NONE, QK_NORM_HEAD, QK_NORM_WHOLE = 0, 1, 2
 DTYPE_CODE = {torch.bfloat16: BF16, torch.float32: F32}
 _lib = None
@@ -51,7 +53,37 @@ class ScanArgs(ctypes.Structure):
                 ("skip", ctypes.c_void_p), ("state", ctypes.c_void_p),
                 ("cu_tok", ctypes.c_void_p), ("past", ctypes.c_void_p), ("slot", ctypes.c_void_p),
                 ("n_seq", ctypes.c_int), ("n_tok", ctypes.c_int), ("out", ctypes.c_void_p),
-                ("seg_state", ctypes.c_void_p), ("seg_decay", ctypes.c_void_p), ("seg_len", ctypes.c_int), ("n_segs", ctypes.c_int)]
+                ("seg_state", ctypes.c_void_p), ("seg_decay", ctypes.c_void_p), ("seg_len", ctypes.c_int), ("n_segs", ctypes.c_int),
+                ("decay_vec", ctypes.c_void_p)]
+
+
+class GluRule(ctypes.Structure):
+    """How a gated feed-forward joins its halves: act(gate) * up, or — act GLU_CAPPED — with g = min(gate, limit) and
+    u = clamp(up, -limit, limit): g * sigmoid(slope * g) * (u + shift)."""
+    _fields_ = [("act", ctypes.c_int), ("limit", ctypes.c_float), ("slope", ctypes.c_float), ("shift", ctypes.c_float)]
+
+    @classmethod
+    def of(cls, act):
+        return act if isinstance(act, cls) else cls(int(act), 0.0, 0.0, 0.0)
+
+    @classmethod
+    def capped(cls, limit, slope, shift):
+        return cls(GLU_CAPPED, float(limit), float(slope), float(shift))
+
+
+class RmsResidualArgs(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("y", ctypes.c_void_p), ("mult", ctypes.c_float),
+                ("hist", ctypes.c_void_p), ("hist_stride", ctypes.c_int64), ("n_hist", ctypes.c_int), ("mix", ctypes.c_void_p),
+                ("mixed", ctypes.c_void_p), ("next_w", ctypes.c_void_p), ("eps", ctypes.c_float), ("next_out", ctypes.c_void_p),
+                ("dtype", ctypes.c_int), ("n_tok", ctypes.c_int), ("width", ctypes.c_int)]
+
+
+class LatentPrepareArgs(ctypes.Structure):
+    _fields_ = [("y", ctypes.c_void_p), ("y_ld", ctypes.c_int64), ("dtype", ctypes.c_int), ("q_col", ctypes.c_int), ("q_rank", ctypes.c_int),
+                ("q_norm_w", ctypes.c_void_p), ("q_out", ctypes.c_void_p), ("q_out_ld", ctypes.c_int64),
+                ("kv_col", ctypes.c_int), ("kv_rank", ctypes.c_int), ("rot_dim", ctypes.c_int), ("rot_dims", ctypes.c_int),
+                ("kv_norm_w", ctypes.c_void_p), ("cos_sin", ctypes.c_void_p), ("eps", ctypes.c_float), ("cache", ctypes.c_void_p),
+                ("cache_row", ctypes.c_int64), ("slot_of_tok", ctypes.c_void_p), ("n_tok", ctypes.c_int)]
 
 class AttnPrepareArgs(ctypes.Structure):
     _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
@@ -69,7 +101,8 @@ class PagedAttentionArgs(ctypes.Structure):
                 ("scale", ctypes.c_float), ("window", ctypes.c_int), ("keep_first", ctypes.c_int), ("sink", ctypes.c_void_p),
                 ("pages", ctypes.c_void_p), ("pages_ld", ctypes.c_int), ("page_size", ctypes.c_int),
                 ("seq_of_tok", ctypes.c_void_p), ("pos_of_tok", ctypes.c_void_p), ("tok_index", ctypes.c_void_p), ("n_tok", ctypes.c_int),
-                ("out", ctypes.c_void_p), ("out_ld", ctypes.c_int64), ("out_scale", ctypes.c_float)]
+                ("out", ctypes.c_void_p), ("out_ld", ctypes.c_int64), ("out_scale", ctypes.c_float),
+                ("k_row", ctypes.c_int64), ("v_row", ctypes.c_int64)]
 
 
 SCAN_SEGMENT = 256                  # tokens per segment when a long portion is scanned as segments side by side
@@ -137,15 +170,31 @@ def activate_cols(x, col0, cols, act):
 
 
 def glu_split(x, act):
+    """act: an activation code (act(gate) * up) or a `GluRule`."""
     T, two = x.shape
     out = torch.empty(T, two // 2, dtype=x.dtype, device=x.device)
-    _ok(lib().mrs_seq_glu_split(_p(x), _p(out), _i(DTYPE_CODE[x.dtype]), _i(T), _i(two // 2), _i(act), _st(x)), "glu_split")
+    rule = GluRule.of(act)
+    _ok(lib().mrs_seq_glu_join(_p(x), _p(out), _i(DTYPE_CODE[x.dtype]), _i(T), _i(two // 2), ctypes.byref(rule), _st(x)), "glu_join")
+    return out
+
+
+def bounded_gate(y, col0, cols, bias, lower):
+    """f32 [T, cols]: lower + (1 - lower) * sigmoid(y[:, col0:col0 + cols] + bias)."""
+    T = y.shape[0]
+    out = torch.empty(T, cols, dtype=torch.float32, device=y.device)
+    _ok(lib().mrs_seq_bounded_gate(_p(y, col0), _l(y.stride(0)), _i(DTYPE_CODE[y.dtype]), _p(bias), _p(lower), _i(T), _i(cols), _p(out), _st(y)),
+        "bounded_gate")
     return out
 
 
 def gated_group_norm(x, gate, gate_col, weight, groups, eps, gate_act, gate_first, out, out_col=0, out_scale=1.0):
     """x f32 [T, C]; the gate is columns gate_col.. of `gate`; writes columns out_col.. of `out`."""
     T, C = x.shape
+    if gate is None:        # no gate: the plain group norm
+        _ok(lib().mrs_seq_gated_group_norm(_p(x), _p(None), _l(0), _p(weight), _p(out, out_col), _l(out.stride(0)), _f(out_scale),
+                                           _i(DTYPE_CODE[out.dtype]), _i(T), _i(C), _i(groups), _f(eps), _i(ACT_NONE), _i(0), _st(x)),
+            "gated_group_norm")
+        return
     _ok(lib().mrs_seq_gated_group_norm(_p(x), _p(gate, gate_col), _l(gate.stride(0)), _p(weight), _p(out, out_col), _l(out.stride(0)),
                                        _f(out_scale), _i(DTYPE_CODE[out.dtype]), _i(T), _i(C), _i(groups), _f(eps), _i(gate_act),
                                        _i(int(gate_first)), _st(x)), "gated_group_norm")
@@ -170,13 +219,17 @@ def ssm_steps(inp, col0, bias, a_log):
 
 
 def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, batch, act=ACT_NONE, decay_tok=None, decay_head=None,
-                scale_tok=None, skip=None):
-    """q / k / v are column ranges (starting at *_col) of 2-D activation tensors; returns o f32 [T, heads * dv]."""
+                scale_tok=None, skip=None, decay_vec=None):
+    """q / k / v are column ranges (starting at *_col) of 2-D activation tensors; returns o f32 [T, heads * dv].
+    decay_vec f32 [T, heads * dk] (then k is None): every state row has its own decay and the key is its complement."""
     T = q.shape[0]
     out = torch.empty(T, heads * dv, dtype=torch.float32, device=q.device)
     a = ScanArgs()
-    a.q, a.k, a.v = _p(q, q_col).value, _p(k, k_col).value, _p(v, v_col).value
-    a.q_ld, a.k_ld, a.v_ld = q.stride(0), k.stride(0), v.stride(0)
+    a.q, a.v = _p(q, q_col).value, _p(v, v_col).value
+    a.q_ld, a.v_ld = q.stride(0), v.stride(0)
+    if k is not None:
+        a.k, a.k_ld = _p(k, k_col).value, k.stride(0)
+    a.decay_vec = _p(decay_vec).value
     a.dtype, a.act = DTYPE_CODE[q.dtype], act
     a.heads, a.qk_groups, a.dk, a.dv = heads, qk_groups, dk, dv
     a.decay_tok, a.decay_head = _p(decay_tok).value, _p(decay_head).value
@@ -185,7 +238,7 @@ def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, b
     a.cu_tok, a.past, a.slot = batch.cu_tok.data_ptr(), batch.past.data_ptr(), batch.slot.data_ptr()
     a.n_seq, a.n_tok, a.out = batch.n_seq, T, out.data_ptr()
     longest = getattr(batch, "longest", 0)
-    if longest >= SCAN_SEGMENT_MIN_TOKENS:
+    if longest >= SCAN_SEGMENT_MIN_TOKENS and decay_vec is None:
         seg = SCAN_SEGMENT
         while batch.n_seq * -(-longest // seg) * heads * dk * dv * 4 > SCAN_SCRATCH_BYTES:
             seg *= 2
@@ -243,15 +296,27 @@ def moe_route(logits, correction, n_groups, keep_groups, top, renorm=False):
     return experts, weights
 
 
+def moe_route_scored(logits, correction, n_groups, keep_groups, top, renorm=False, score_fn=SCORE_SOFTMAX, group_top=1, weight_scale=1.0):
+    """`moe_route` with its choices open: softmax or sigmoid scores, a group scored by the sum of its group_top largest
+    choices, weights times weight_scale."""
+    T, E = logits.shape
+    experts = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _ok(lib().mrs_seq_moe_route_scored(_p(logits), _p(correction), _i(T), _i(E), _i(n_groups), _i(keep_groups), _i(top), _i(int(renorm)),
+                                       _i(score_fn), _i(group_top), _f(weight_scale), _p(experts), _p(weights), _st(logits)), "moe_route_scored")
+    return experts, weights
+
+
 def moe_small(x, gate_up, down, experts, weights, act):
-    """Expert feed-forward by weight streaming (few tokens): gate_up [E, 2ff, W], down [E, W, ff]."""
+    """Expert feed-forward by weight streaming (few tokens): gate_up [E, 2ff, W], down [E, W, ff]; act: a code or a `GluRule`."""
     T, W = x.shape
     top, ff = experts.shape[1], down.shape[2]
     code = _i(DTYPE_CODE[x.dtype])
     hidden = torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
     out = torch.empty(T, W, dtype=x.dtype, device=x.device)
-    _ok(lib().mrs_seq_moe_gate_up(_p(x), _p(gate_up), code, _p(experts), _i(T), _i(top), _i(W), _i(ff), _i(act), _p(hidden), _st(x)),
-        "moe_gate_up")
+    rule = GluRule.of(act)
+    _ok(lib().mrs_seq_moe_gate_up_rule(_p(x), _p(gate_up), code, _p(experts), _i(T), _i(top), _i(W), _i(ff), ctypes.byref(rule), _p(hidden),
+                                       _st(x)), "moe_gate_up")
     _ok(lib().mrs_seq_moe_down(_p(hidden), _p(down), code, _p(experts), _p(weights), _i(T), _i(top), _i(W), _i(ff), _p(out), _st(x)),
         "moe_down")
     return out
@@ -330,10 +395,12 @@ def attention_prepare(y, q_col, k_col, v_col, norm_mode, q_norm_w, k_norm_w, eps
 
 
 def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, keep_first, sink, batch, page_size, out, out_col=0,
-                    out_scale=1.0, tok_index=None):
+                    out_scale=1.0, tok_index=None, k_row=0, v_row=0):
     """Every token of the step (or those listed in tok_index) against the pages of its sequence: position i sees j <= i
-    with i - j < window (0: all) or j < keep_first; sink [heads] f32 or None."""
+    with i - j < window (0: all) or j < keep_first; sink [heads] f32 or None.  k_row / v_row: elements between the cache
+    rows of neighbouring slots (0: kv_heads * dk / kv_heads * dv)."""
     a = PagedAttentionArgs()
+    a.k_row, a.v_row = int(k_row), int(v_row)
     a.q, a.q_ld, a.k_cache, a.v_cache = _p(y, q_col).value, y.stride(0), k_cache.data_ptr(), v_cache.data_ptr()
     a.dtype, a.heads, a.kv_heads, a.dk, a.dv = DTYPE_CODE[y.dtype], heads, kv_heads, dk, dv
     a.scale, a.window, a.keep_first, a.sink = scale, int(window), int(keep_first), _p(sink).value
@@ -400,3 +467,59 @@ def moe_small_ungated(x, up, down, experts, weights, act):
     _ok(lib().mrs_seq_moe_down(_p(hidden), _p(down), code, _p(experts), _p(weights), _i(T), _i(top), _i(W), _i(ff), _p(out), _st(x)),
         "moe_down")
     return out
+
+
+# ---- single residual with RMS norms, a multiplier and a depth-weighted average ---------------------------------
+def embed_scaled(table, ids, scale, out):
+    """out f32 [T, W] = table[ids] * scale."""
+    T, W = ids.numel(), table.shape[1]
+    _ok(lib().mrs_seq_embed_scaled(_p(table), _i(DTYPE_CODE[table.dtype]), _p(ids), _f(scale), _p(out), _i(T), _i(W), _st(table)), "embed_scaled")
+    return out
+
+
+def rms_residual(src, y=None, mult=1.0, dst=None, hist=None, n_hist=0, mix=None, mixed=None, next_w=None, eps=0.0, dtype=None):
+    """One pass over an f32 residual [T, W]: v = src + mult * y -> dst; v = sum_j mix[j] * hist[j] (hist f32 [>= n_hist, T, W],
+    dst may be one of its entries) -> mixed; returns rms_norm(v) * next_w in the activation type when next_w is given."""
+    T, W = src.shape
+    dtype = y.dtype if y is not None else dtype
+    out = torch.empty(T, W, dtype=dtype, device=src.device) if next_w is not None else None
+    a = RmsResidualArgs()
+    a.src, a.dst, a.y, a.mult = _p(src).value, _p(dst).value, _p(y).value, float(mult)
+    if hist is not None:
+        a.hist, a.hist_stride, a.n_hist, a.mix = _p(hist).value, hist.stride(0), int(n_hist), _p(mix).value
+    a.mixed, a.next_w, a.eps, a.next_out = _p(mixed).value, _p(next_w).value, float(eps), _p(out).value
+    a.dtype, a.n_tok, a.width = DTYPE_CODE[dtype], T, W
+    _ok(lib().mrs_seq_rms_residual(ctypes.byref(a), _st(src)), "rms_residual")
+    return out
+
+
+# ---- attention through a shared latent -----------------------------------------------------------------------
+def latent_prepare(y, q_col, q_rank, q_norm_w, q_out, kv_col, kv_rank, rot_dim, rot_dims, kv_norm_w, cos_sin, eps, cache, slot_of_tok):
+    """From the columns of y: q_out = rms_norm(query latent) * w; cache[slot] = rms_norm(key/value latent) * w | the shared key
+    part turned in neighbouring pairs.  kv_rank 0: only the query part."""
+    a = LatentPrepareArgs()
+    a.y, a.y_ld, a.dtype = _p(y).value, y.stride(0), DTYPE_CODE[y.dtype]
+    a.q_col, a.q_rank, a.q_norm_w = int(q_col), int(q_rank), _p(q_norm_w).value
+    if q_out is not None:
+        a.q_out, a.q_out_ld = _p(q_out).value, q_out.stride(0)
+    a.kv_col, a.kv_rank, a.rot_dim, a.rot_dims = int(kv_col), int(kv_rank), int(rot_dim), int(rot_dims)
+    a.kv_norm_w, a.cos_sin, a.eps = _p(kv_norm_w).value, _p(cos_sin).value, float(eps)
+    if kv_rank:
+        a.cache, a.cache_row, a.slot_of_tok = _p(cache).value, cache.stride(0), _p(slot_of_tok).value
+    a.n_tok = y.shape[0]
+    _ok(lib().mrs_seq_latent_prepare(ctypes.byref(a), _st(y)), "latent_prepare")
+
+
+def rotate_pairs(src, src_col, src_head, dst, dst_col, dst_head, heads, dims, rot_dims, cos_sin):
+    """dst[t, dst_col + h * dst_head + d] = src[t, src_col + h * src_head + d], d < dims, the first rot_dims turned in
+    neighbouring pairs by cos_sin [T, rot_dims / 2, 2]."""
+    _ok(lib().mrs_seq_rotate_pairs(_p(src, src_col), _l(src.stride(0)), _l(src_head), _p(dst, dst_col), _l(dst.stride(0)), _l(dst_head),
+                                   _i(DTYPE_CODE[src.dtype]), _i(heads), _i(dims), _i(rot_dims), _p(cos_sin), _i(src.shape[0]), _st(src)),
+        "rotate_pairs")
+
+
+def latent_attention(qa, latent, heads, kv_rank, rot_dim, scale, window, batch, page_size, out, tok_index=None):
+    """Absorbed latent attention of every token of the step: qa [T, heads * (kv_rank + rot_dim)] against the cached latent
+    rows [slots, >= kv_rank + rot_dim] as one key/value head (values = the rows' first kv_rank columns); out [T, heads * kv_rank]."""
+    paged_attention(qa, 0, latent, latent, heads, 1, kv_rank + rot_dim, kv_rank, scale, window, 0, None, batch, page_size, out,
+                    tok_index=tok_index, k_row=latent.stride(0), v_row=latent.stride(0))
