@@ -263,6 +263,17 @@ int mrs_seq_latent_prepare(const mrs_seq_latent_prepare_args *args, int64_t stre
 int mrs_seq_rotate_pairs(const void *in, int64_t in_ld, int64_t in_head, void *out, int64_t out_ld, int64_t out_head, int dtype,
                          int heads, int dims, int rot_dims, const float *cos_sin, int n_tok, int64_t stream);
 
+/* The long portions of a step on tensor cores, in the absorbed form: q [n_tok, heads, kv_rank + rot_dim] (row stride q_ld) holds
+ * per head [W_uk^T q_plain | q_rot]; the cached rows (cache_row elements apart) are at once the keys (all kv_rank + rot_dim
+ * columns) and the values (the first kv_rank columns) of every head; out [n_tok, heads, kv_rank] (row stride out_ld).
+ * Position i sees j with 0 <= i - j < window (window <= 0: every earlier position).  portions / longest / pages as for
+ * mrs_seq_prompt_attention.  bf16; kv_rank and kv_rank + rot_dim multiples of 8; mrs_seq_latent_attention_fits tells
+ * whether the sizes fit the kernel's shared memory (else: mrs_seq_paged_attention with row strides). */
+int mrs_seq_latent_attention_fits(int kv_rank, int rot_dim);
+int mrs_seq_latent_attention(const void *q, int64_t q_ld, const void *cache, int64_t cache_row, void *out, int64_t out_ld,
+                             const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
+                             int page_size, int heads, int kv_rank, int rot_dim, float scale, int window, int64_t stream);
+
 /* x[r][c] *= scale for r < rows, c < cols (row stride ld) */
 int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream);
 

@@ -217,11 +217,12 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     const int n = min(32, jend - j0);
     // eight keys per pass: their value rows are fetched together, so the loads overlap instead of queueing behind the
     // shuffles that carry each key's slot
-    for (int i0 = 0; i0 < n; i0 += 8) {
-      float pi[8];
-      float2 vv[8][VPAIRS];
+    constexpr int KPP = VPAIRS > 4 ? 4 : 8;       // keys per pass: fewer for wide values, whose rows fill the registers sooner
+    for (int i0 = 0; i0 < n; i0 += KPP) {
+      float pi[KPP];
+      float2 vv[KPP][VPAIRS];
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
+      for (int u = 0; u < KPP; u++) {
         const int i = min(i0 + u, 31);
         const float pu = __shfl_sync(0xffffffffu, p, i);
         pi[u] = i0 + u < n ? pu : 0.0f;
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
           vv[u][c] = c * 64 + 2 * lane < dv ? load2<T>(vr + c * 64 + 2 * lane) : make_float2(0.0f, 0.0f);
       }
 #pragma unroll
-      for (int u = 0; u < 8; u++)
+      for (int u = 0; u < KPP; u++)
 #pragma unroll
         for (int c = 0; c < VPAIRS; c++) {
           acc[c].x = fmaf(pi[u], vv[u][c].x, acc[c].x);
@@ -313,12 +314,12 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
   const mrs_seq_paged_attention_args &a = *args;
   const int n_tok = a.n_tok, heads = a.heads, kv_heads = a.kv_heads, dk = a.dk, dv = a.dv, dtype = a.dtype;
   if (n_tok <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 512 || dk > 1024 || a.page_size <= 0) return -2;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 1024 || dk > 2048 || a.page_size <= 0) return -2;
   const int keep_first = a.keep_first > 0 ? a.keep_first : 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
   const int64_t k_row = a.k_row > 0 ? a.k_row : (int64_t)kv_heads * dk, v_row = a.v_row > 0 ? a.v_row : (int64_t)kv_heads * dv;
-  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 256 && ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 8) == 0 &&
+  const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 512 && ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 8) == 0 &&
                    k_row % (16 / elem) == 0 && v_row % 2 == 0;
   if (vec) {
     constexpr int SPLIT = 8;
@@ -329,7 +330,8 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
     SEQ_DISPATCH_DTYPE(dtype, {
       if (dv <= 64) SEQ_ATTN_VEC(1);
       else if (dv <= 128) SEQ_ATTN_VEC(2);
-      else SEQ_ATTN_VEC(4);
+      else if (dv <= 256) SEQ_ATTN_VEC(4);
+      else SEQ_ATTN_VEC(8);
     });
 #undef SEQ_ATTN_VEC
     return launch_status();
@@ -344,7 +346,8 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
     if (dv <= 64) SEQ_ATTN_LAUNCH(2);
     else if (dv <= 128) SEQ_ATTN_LAUNCH(4);
     else if (dv <= 256) SEQ_ATTN_LAUNCH(8);
-    else SEQ_ATTN_LAUNCH(16);
+    else if (dv <= 512) SEQ_ATTN_LAUNCH(16);
+    else SEQ_ATTN_LAUNCH(32);
   });
 #undef SEQ_ATTN_LAUNCH
   return launch_status();

@@ -518,6 +518,19 @@ def rotate_pairs(src, src_col, src_head, dst, dst_col, dst_head, heads, dims, ro
         "rotate_pairs")
 
 
+def latent_attention_fits(kv_rank, rot_dim):
+    """True when the tensor-core latent kernel takes these sizes (bf16 only)."""
+    return bool(lib().mrs_seq_latent_attention_fits(_i(kv_rank), _i(rot_dim)))
+
+
+def latent_prompt_attention(qa, latent, heads, kv_rank, rot_dim, scale, window, batch, page_size, out):
+    """The long portions of the step (batch.long) of the absorbed latent attention on tensor cores."""
+    _ok(lib().mrs_seq_latent_attention(_p(qa), _l(qa.stride(0)), _p(latent), _l(latent.stride(0)), _p(out), _l(out.stride(0)),
+                                       _p(batch.long_rows), _i(len(batch.long)), _i(max(n for _, n, _, _ in batch.long)), _p(batch.pages),
+                                       _i(batch.pages.shape[1]), _i(page_size), _i(heads), _i(kv_rank), _i(rot_dim), _f(scale), _i(int(window)),
+                                       _st(qa)), "latent_attention")
+
+
 def latent_attention(qa, latent, heads, kv_rank, rot_dim, scale, window, batch, page_size, out, tok_index=None):
     """Absorbed latent attention of every token of the step: qa [T, heads * (kv_rank + rot_dim)] against the cached latent
     rows [slots, >= kv_rank + rot_dim] as one key/value head (values = the rows' first kv_rank columns); out [T, heads * kv_rank]."""
