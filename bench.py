@@ -764,6 +764,198 @@ def bench_kilizen(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
     return out
 
 
+# ------------------------------------------------------------------------------------------- --arch fosulix
+def fosulix_bench_config(width, vocab=32000):
+    """Four layers at sizes of a real model's layers of this width: latent attention that forms its latent, a tied-gate
+    recurrence, latent attention that reuses the first layer's latent, a second recurrence; routed experts everywhere."""
+    H = width // 128
+    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    lat = {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 4, "kv_rank": 512, "scale": 192 ** -0.5, "rot": rot,
+           "mask": {"size": 1024}}
+    rec = {"heads": H, "dim": 128, "vdim": 128}
+    moe = {"kind": "moe", "expert": {"ff": width, "limit": 7.0}, "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Fosulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "embedding": {"scale": width ** 0.5},
+            "canon": {"taps": 4},
+            "layers": [{"type": "latent_attention", "mixer": lat, "mlp": moe}, {"type": "hgrn2", "mixer": rec, "mlp": moe},
+                       {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": moe}, {"type": "hgrn2", "mixer": rec, "mlp": moe}]}
+
+
+def bench_fosulix(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), prompt=4096, decode_batches=(1, 32)):
+    """Prefill and decode throughput of the Fosulix design through `engine.Engine.execute` at layer sizes of a real model,
+    and of the Kilizen design (the closest model: one f32 residual, windowed attention with scaled rotary positions, a
+    linear recurrence, routed experts, same engine and kernel library) at equal width / depth / head sizes; then, per
+    kernel, the achieved fraction of the measured HBM rate (or f32 / tensor TFLOP/s) beside the like kernel of Kilizen.
+    CUDA events, L2 flushed between repetitions."""
+    import numpy as np
+    from mistralrs_b200 import engine, fosulix, kilizen, mixers, seq_ops as K
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    tpeak = peaks.get("bf16_tflops_sustained", 1400.0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    warmup, steps = max(3, warmup), max(1, steps)
+    names = ["embed_streams", "embed_scaled", "streams_read_norm", "rms_residual", "glu_split", "gated_group_norm", "causal_conv", "linear_scan",
+             "activate_cols", "bounded_gate", "latent_prepare", "rotate_pairs", "latent_prompt_attention", "paged_attention", "prompt_attention",
+             "fresh_prompt_attention", "attention_prepare", "rotation_table", "moe_route", "moe_route_scored", "moe_route_top_softmax", "moe_small",
+             "moe_small_ungated", "moe_sort", "moe_gather", "moe_combine", "tanh_norm_rows", "residual_tanh_norm", "mlstm_gates", "append_ones",
+             "mlstm_out_norm", "scale_rows"]
+
+    def timed(fn, reps=steps):
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        return sorted(ts)[len(ts) // 2]
+
+    def by_op(fn):
+        """One call of fn with CUDA events around every kernel wrapper and every library product of the mixers."""
+        acc, saved = {}, {}
+
+        def wrap(mod, name):
+            f = getattr(mod, name)
+
+            def g(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = f(*a, **k)
+                e1.record()
+                acc.setdefault(name, []).append((e0, e1))
+                return r
+            setattr(mod, name, g)
+            saved[(mod, name)] = f
+        for n in names:
+            wrap(K, n)
+        wrap(mixers, "linear")
+        wrap(torch, "bmm")
+        wrap(torch, "mm")
+        try:
+            torch.cuda.synchronize()
+            flush.zero_()
+            fn()
+            torch.cuda.synchronize()
+        finally:
+            for (mod, name), f in saved.items():
+                setattr(mod, name, f)
+        return {n: round(sum(a.elapsed_time(b) for a, b in v), 4) for n, v in acc.items()}
+
+    def measure(model, vocab, rng):
+        row = {}
+        eng = engine.Engine(model, max_tokens=max(prompt, 32 * (prompt // 8 + 64)) + 64, max_seqs=max(decode_batches))
+        toks = rng.integers(0, vocab, prompt).tolist()
+
+        def prefill():
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt)])
+            eng.finish(r)
+        t = timed(prefill)
+        row["prefill_tok_s"], row["prefill_ms"] = prompt / t, t * 1e3
+        row["prefill_ms_by_op"] = by_op(prefill)
+
+        def prefill_cut():                                   # the same prompt in two steps: the second portion continues the sequence
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt // 2)])
+            eng.execute([(r, prompt - prompt // 2)])
+            eng.finish(r)
+        row["prefill_two_portions_ms"] = timed(prefill_cut) * 1e3
+        row["decode"] = []
+        ctx = prompt // 8
+        for b in decode_batches:
+            reqs = [eng.new_request(rng.integers(0, vocab, ctx + 64).tolist()) for _ in range(b)]
+            eng.execute([(r, ctx) for r in reqs])
+
+            def dec():
+                eng.execute([(r, 1) for r in reqs])
+            t = timed(dec, reps=max(steps, 5))
+            eng.decode_graphs, graphs = False, eng.decode_graphs          # the per-op table needs the eager step
+            ops = by_op(dec)
+            eng.decode_graphs = graphs
+            row["decode"].append({"batch": b, "context": ctx, "tok_s": b / t, "ms_per_step": t * 1e3, "graph": b in eng._graphs, "ms_by_op": ops})
+            for r in reqs:
+                eng.finish(r)
+        del eng
+        torch.cuda.empty_cache()
+        return row
+
+    out = {"metric": "fosulix_prefill_tok_s", "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True,
+           "dtype": "bf16 (f32 residual, states, gates, norms, softmax, router)", "data": "synthetic", "sizes": []}
+    for width in widths:
+        rng = np.random.default_rng(width)
+        cj = fosulix_bench_config(width)
+        cfg = fosulix.FosulixConfig(cj)
+        model = fosulix.FosulixModel.random(cfg, dev, torch.bfloat16, seed=width)
+        row = {"width": width, "layers": len(cj["layers"]), "prompt_tokens": prompt}
+        row.update(measure(model, cfg.vocab, rng))
+        del model
+        torch.cuda.empty_cache()
+        kcj = kilizen_bench_config(width)
+        kcfg = kilizen.KilizenConfig(kcj)
+        kmodel = kilizen.KilizenModel.random(kcfg, dev, torch.bfloat16, seed=width)
+        row["kilizen_equal_size"] = near = measure(kmodel, kcfg.vocab, rng)
+        del kmodel
+        torch.cuda.empty_cache()
+        # ---- per kernel: achieved rate on the algorithmic bytes / flops of the prefill, beside the like kernel ----
+        T, W, H, d = prompt, width, width // 128, 128
+        lat = cj["layers"][0]["mixer"]
+        R, dr, qr, win = lat["kv_rank"], lat["rot_dim"], lat["q_rank"], lat["mask"]["size"]
+        ops, kops = row["prefill_ms_by_op"], near["prefill_ms_by_op"]
+        gbs = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9 / hbm if ms else None
+        tfl = lambda flop, ms: flop / (ms * 1e-3) / 1e12 if ms else None
+        roof = {}
+        # residual pass: source read + result written (f32), y read, next input written (bf16); the layer's last pass also reads the
+        # history (i + 2 entries for layer i, its own entry fresh) and writes the average.  Four layers, two passes each, one first norm.
+        res = 8 * T * W * (4 + 4 + 2 + 2) + sum((i + 1) * T * W * 4 + T * W * 4 for i in range(4)) + T * W * (4 + 2)
+        roof["rms_residual"] = {"ms": ops.get("rms_residual"), "hbm_frac": gbs(res, ops.get("rms_residual")), "like": "residual_tanh_norm",
+                                "like_hbm_frac": gbs(8 * T * W * (4 + 4 + 2 + 2) - T * W * 2, kops.get("residual_tanh_norm"))}
+        roof["causal_conv"] = {"ms": ops.get("causal_conv"), "hbm_frac": gbs(4 * T * W * (2 + 2), ops.get("causal_conv")), "like": "none (Kilizen has no convolution)"}
+        # latent preparation: the projection's latent columns read, query latent written, latent row written; then the rotated query parts
+        prep = T * 2 * (2 * qr + R + dr) + T * 2 * (R + dr) + T * 2 * 2 * qr + 2 * T * H * dr * 2 * 2
+        G = max(1, H // 4)
+        roof["latent_prepare + rotate_pairs"] = {"ms": ops.get("latent_prepare", 0.0) + ops.get("rotate_pairs", 0.0),
+                                                 "hbm_frac": gbs(prep, ops.get("latent_prepare", 0.0) + ops.get("rotate_pairs", 0.0)), "like": "attention_prepare",
+                                                 "like_hbm_frac": gbs(2 * T * 2 * (2 * H * d + 2 * G * d + 2 * G * d) + T * 2 * G * d * 2, kops.get("attention_prepare"))}
+        seen = sum(min(i + 1, win) for i in range(T))
+        lflop = 2 * 2.0 * H * ((R + dr) + R) * seen                   # two latent layers; per (query, key, head): dk + dv multiply-adds
+        kwin, keep = kcj["layers"][2]["mixer"]["mask"]["size"], kcj["layers"][2]["mixer"]["mask"]["keep_first"]
+        kflop = 4.0 * H * d * T * (T + 1) / 2 + 4.0 * H * d * sum(min(i + 1, kwin) + min(keep, max(0, i + 1 - kwin)) for i in range(T))
+        roof["latent_prompt_attention"] = {"ms": ops.get("latent_prompt_attention"), "tflops": tfl(lflop, ops.get("latent_prompt_attention")),
+                                           "tensor_frac": (tfl(lflop, ops.get("latent_prompt_attention")) or 0.0) / tpeak, "like": "prompt_attention",
+                                           "like_tflops": tfl(kflop, kops.get("prompt_attention")), "like_tensor_frac": (tfl(kflop, kops.get("prompt_attention")) or 0.0) / tpeak}
+        dvp = -(-(d + 1) // 8) * 8
+        roof["linear_scan (per-row decay)"] = {"ms": ops.get("linear_scan"), "tflops_f32": tfl(2 * T * H * 5.0 * d * d, ops.get("linear_scan")), "like": "linear_scan",
+                                               "like_tflops_f32": tfl(2 * T * H * 4.0 * d * dvp, kops.get("linear_scan"))}
+        roof["bounded_gate"] = {"ms": ops.get("bounded_gate"), "hbm_frac": gbs(2 * T * H * d * (2 + 4), ops.get("bounded_gate")), "like": "mlstm_gates + append_ones",
+                                "like_ms": kops.get("mlstm_gates", 0.0) + kops.get("append_ones", 0.0)}
+        roof["gated_group_norm"] = {"ms": ops.get("gated_group_norm"), "hbm_frac": gbs(2 * T * H * d * (4 + 2), ops.get("gated_group_norm")), "like": "mlstm_out_norm",
+                                    "like_hbm_frac": gbs(2 * T * H * (dvp * 4 + d * 2 + d * 2), kops.get("mlstm_out_norm"))}
+        roof["moe_route_scored"] = {"ms": ops.get("moe_route_scored"), "like": "moe_route_top_softmax", "like_ms": kops.get("moe_route_top_softmax")}
+        roof["glu_split"] = {"ms": ops.get("glu_split"), "hbm_frac": gbs(4 * T * 2 * W * (2 * 2 + 2), ops.get("glu_split")), "like": "activate_cols",
+                             "like_ms": kops.get("activate_cols")}
+        roof["library products (linear + bmm + mm)"] = {"ms": ops.get("linear", 0.0) + ops.get("bmm", 0.0) + ops.get("mm", 0.0),
+                                                       "like_ms": kops.get("linear", 0.0) + kops.get("bmm", 0.0) + kops.get("mm", 0.0)}
+        for bi, b in enumerate(decode_batches):
+            dk = row["decode"][bi]["ms_by_op"], near["decode"][bi]["ms_by_op"]
+            ctx = prompt // 8
+            # per token and layer the window's latent rows are read once whatever the head count (they sit in L2 for the other heads)
+            lbytes = 2 * b * min(ctx, win) * (R + dr) * 2
+            kbytes = b * (2 * G * d * 2 * ctx + 2 * G * d * 2 * min(ctx, kwin))
+            roof["paged_attention (decode, b=%d)" % b] = {"ms": dk[0].get("paged_attention"), "hbm_frac": gbs(lbytes, dk[0].get("paged_attention")),
+                                                          "like": "paged_attention", "like_ms": dk[1].get("paged_attention"),
+                                                          "like_hbm_frac": gbs(kbytes, dk[1].get("paged_attention"))}
+        row["roofline"] = roof
+        out["sizes"].append(row)
+    out["value"] = out["sizes"][0]["prefill_tok_s"]
+    out["ms_per_step"] = out["sizes"][0]["prefill_ms"]
+    out["config"] = {"workload": "4 layers (latent attention, tied-gate recurrence, latent attention on the first layer's latent, recurrence; routed experts "
+                                 "in every layer), widths %s, %d-token prompt; decode at context %d; Kilizen at equal sizes beside it; L2 flushed between "
+                                 "repetitions" % (list(widths), prompt, prompt // 8)}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -773,10 +965,11 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="headline workload: 1 = TinyLlama-1.1B Q4_K_M on the CPU (plumbing, no GPU), 2 = 8B Q4_K_M decode b=1 (default), "
                          "3 = 8B Q8_0 prefill 4096, 4 = Mistral-7B GPTQ b=32, 5 = Llama-3-70B Q4_K_M tensor parallel (needs --gpus 8)")
-    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun", "kilizen"],
+    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun", "kilizen", "fosulix"],
                     help="nisasun: prefill / decode throughput of the Nisasun design on the step engine at layer sizes of a real model "
                          "(random weights), beside the Llama path at equal width / depth / feed-forward size, with a per-kernel table; "
-                         "kilizen: the same for the Kilizen design, beside Nisasun at equal sizes")
+                         "kilizen: the same for the Kilizen design, beside Nisasun at equal sizes; "
+                         "fosulix: the same for the Fosulix design, beside Kilizen at equal sizes")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model")
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("MRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -816,6 +1009,9 @@ def main():
         return
     if args.arch == "kilizen":
         print(json.dumps(bench_kilizen(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
+        return
+    if args.arch == "fosulix":
+        print(json.dumps(bench_fosulix(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
         return
     if args.config == 3 and world == 1:
         pf = bench_prefill_q8(M, torch, dev, peaks, layers=args.layers)

@@ -123,7 +123,8 @@ int mrs_seq_ssm_steps(const void *in, int64_t in_ld, int col0, int dtype, const 
  *   o_t = S_t^T q_t + skip[h] v_t         (o f32 [n_tok, heads * dv])
  * a_t = decay_tok[t][h] (or decay_head[h] when decay_tok is NULL), b_t = scale_tok[t][h] (1 when NULL), skip NULL: 0.
  * decay_vec f32 [n_tok, heads, dk] (then decay_tok, decay_head and k are NULL and qk_groups == heads): every state row has
- * its own decay and the key is its complement, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; such portions run in one pass.
+ * its own decay and the key is its complement, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; seg_decay then holds one product
+ * per state row, f32 [n_seq * n_segs, heads, dk].
  * q, k: [n_tok, qk_groups, dk] with row strides q_ld / k_ld; v: [n_tok, heads, dv] with row stride v_ld; `act` is
  * applied to q, k and v as they are read.
  * Long portions can run as n_segs segments of seg_len tokens side by side (n_segs > 1): the caller provides
@@ -267,12 +268,14 @@ int mrs_seq_rotate_pairs(const void *in, int64_t in_ld, int64_t in_head, void *o
  * per head [W_uk^T q_plain | q_rot]; the cached rows (cache_row elements apart) are at once the keys (all kv_rank + rot_dim
  * columns) and the values (the first kv_rank columns) of every head; out [n_tok, heads, kv_rank] (row stride out_ld).
  * Position i sees j with 0 <= i - j < window (window <= 0: every earlier position).  portions / longest / pages as for
- * mrs_seq_prompt_attention.  bf16; kv_rank and kv_rank + rot_dim multiples of 8; mrs_seq_latent_attention_fits tells
+ * mrs_seq_prompt_attention; portions NULL: every sequence of the step is one portion (cu_tok / past as for the scan,
+ * n_portions = n_seq, page-table row = sequence), decoded tokens included.  bf16; kv_rank and kv_rank + rot_dim multiples of 8; mrs_seq_latent_attention_fits tells
  * whether the sizes fit the kernel's shared memory (else: mrs_seq_paged_attention with row strides). */
 int mrs_seq_latent_attention_fits(int kv_rank, int rot_dim);
 int mrs_seq_latent_attention(const void *q, int64_t q_ld, const void *cache, int64_t cache_row, void *out, int64_t out_ld,
-                             const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
-                             int page_size, int heads, int kv_rank, int rot_dim, float scale, int window, int64_t stream);
+                             const int32_t *portions, const int32_t *cu_tok, const int32_t *past, int n_portions, int longest,
+                             const int32_t *pages, int pages_ld, int page_size, int heads, int kv_rank, int rot_dim, float scale,
+                             int window, int64_t stream);
 
 /* x[r][c] *= scale for r < rows, c < cols (row stride ld) */
 int mrs_seq_scale_rows(void *x, int64_t ld, int dtype, int rows, int cols, float scale, int64_t stream);

@@ -52,21 +52,30 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const mrs_seq_laten
   for (int d = 2 * half + threadIdx.x; d < a.rot_dim; d += blockDim.x) dst[d] = src[d];
 }
 
-// grid (token, head): out[t][h][:dims] = in[t][h][:dims] with the first rot_dims entries turned in neighbouring pairs
+// one CTA per token, all heads: out[t][h][:dims] = in[t][h][:dims] with the first rot_dims entries turned in neighbouring pairs
 template <typename T>
 __global__ void rotate_pairs_kernel(const T *__restrict__ in, int64_t in_ld, int64_t in_head, T *__restrict__ out, int64_t out_ld,
-                                    int64_t out_head, int dims, int rot_dims, const float2 *__restrict__ cos_sin) {
-  const int t = blockIdx.x, h = blockIdx.y, half = cos_sin ? rot_dims / 2 : 0;
-  const T *src = in + (int64_t)t * in_ld + (int64_t)h * in_head;
-  T *dst = out + (int64_t)t * out_ld + (int64_t)h * out_head;
+                                    int64_t out_head, int heads, int dims, int rot_dims, const float2 *__restrict__ cos_sin) {
+  const int t = blockIdx.x, half = cos_sin ? rot_dims / 2 : 0, pairs = dims / 2;
+  const T *src = in + (int64_t)t * in_ld;
+  T *dst = out + (int64_t)t * out_ld;
   const float2 *cs = cos_sin + (int64_t)t * half;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float u = to_f32<T>(src[2 * i]), v = to_f32<T>(src[2 * i + 1]);
-    const float2 c = cs[i];
-    dst[2 * i] = from_f32<T>(u * c.x - v * c.y);
-    dst[2 * i + 1] = from_f32<T>(v * c.x + u * c.y);
+  for (int e = threadIdx.x; e < heads * pairs; e += blockDim.x) {
+    const int h = e / pairs, i = e % pairs;
+    const T *s = src + (int64_t)h * in_head + 2 * i;
+    T *d = dst + (int64_t)h * out_head + 2 * i;
+    if (i < half) {
+      const float u = to_f32<T>(s[0]), v = to_f32<T>(s[1]);
+      const float2 c = cs[i];
+      d[0] = from_f32<T>(u * c.x - v * c.y);
+      d[1] = from_f32<T>(v * c.x + u * c.y);
+    } else {
+      d[0] = s[0];
+      d[1] = s[1];
+    }
   }
-  for (int d = 2 * half + threadIdx.x; d < dims; d += blockDim.x) dst[d] = src[d];
+  if (dims & 1)
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) dst[(int64_t)h * out_head + dims - 1] = src[(int64_t)h * in_head + dims - 1];
 }
 
 }  // namespace seq
@@ -90,8 +99,8 @@ extern "C" int mrs_seq_rotate_pairs(const void *in, int64_t in_ld, int64_t in_he
                                     int heads, int dims, int rot_dims, const float *cos_sin, int n_tok, int64_t stream) {
   if (n_tok <= 0 || heads <= 0 || dims <= 0) return 0;
   if (cos_sin && (rot_dims < 2 || rot_dims % 2 || rot_dims > dims)) return -2;
-  const int th = dims >= 128 ? 64 : 32;
-  SEQ_DISPATCH_DTYPE(dtype, (rotate_pairs_kernel<T><<<dim3(n_tok, heads), th, 0, (cudaStream_t)stream>>>(
-                                (const T *)in, in_ld, in_head, (T *)out, out_ld, out_head, dims, rot_dims, (const float2 *)cos_sin)));
+  const int items = heads * (dims / 2), th = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+  SEQ_DISPATCH_DTYPE(dtype, (rotate_pairs_kernel<T><<<n_tok, th, 0, (cudaStream_t)stream>>>(
+                                (const T *)in, in_ld, in_head, (T *)out, out_ld, out_head, heads, dims, rot_dims, (const float2 *)cos_sin)));
   return launch_status();
 }

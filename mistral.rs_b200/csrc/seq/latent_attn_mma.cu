@@ -13,6 +13,8 @@
 //   C  O = O * rescale + P V: warp w takes row tile w % MT and one of 8 / MT column groups of the kv_rank output columns
 //      (at most 128 columns, 64 accumulator registers), V fragments are transposed loads of the same key tile.
 // MT = 4, 2, 1 for kv_rank up to 256, 512, 1024.  bf16 only; dk and kv_rank multiples of 8.
+// A decoded token is a portion of one token: its heads are the rows of one tile and the window's latents are fetched once
+// for all of them, where a (token, head) kernel fetches them once per head.
 #include "../mma_common.cuh"
 
 #include "../../../include/mrs_b200_seq.h"
@@ -26,7 +28,8 @@ struct Params {
   const __nv_bfloat16 *q, *cache;
   __nv_bfloat16 *o;
   int64_t q_ld, o_ld, cache_row;
-  const int32_t *portions;     // [n][4]: first token row, tokens, positions cached before (past), row of the page table
+  const int32_t *portions;     // [n][4]: first token row, tokens, positions cached before (past), row of the page table; or NULL:
+  const int32_t *cu_tok, *past;   // every sequence of the step — tokens cu_tok[b] .. cu_tok[b + 1], past[b] cached before, table row b
   const int32_t *pages;
   int pages_ld, page_size;
   int H, DK, R;
@@ -47,8 +50,9 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_mma_kernel(const 
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.y;
-  const int tok0 = p.portions[4 * b], len = p.portions[4 * b + 1], past = p.portions[4 * b + 2];
-  const int32_t *table = p.pages + (int64_t)p.portions[4 * b + 3] * p.pages_ld;
+  const int tok0 = p.portions ? p.portions[4 * b] : p.cu_tok[b], len = p.portions ? p.portions[4 * b + 1] : p.cu_tok[b + 1] - tok0;
+  const int past = p.portions ? p.portions[4 * b + 2] : p.past[b];
+  const int32_t *table = p.pages + (int64_t)(p.portions ? p.portions[4 * b + 3] : b) * p.pages_ld;
   const int n_rows = len * p.H, row0 = blockIdx.x * BM;
   if (row0 >= n_rows) return;
   const int tok_lo = row0 / p.H, tok_hi = min(len - 1, (row0 + BM - 1) / p.H);
@@ -224,20 +228,26 @@ extern "C" int mrs_seq_latent_attention_fits(int kv_rank, int rot_dim) {
 }
 
 extern "C" int mrs_seq_latent_attention(const void *q, int64_t q_ld, const void *cache, int64_t cache_row, void *out, int64_t out_ld,
-                                        const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
-                                        int page_size, int heads, int kv_rank, int rot_dim, float scale, int window, int64_t stream) {
+                                        const int32_t *portions, const int32_t *cu_tok, const int32_t *past, int n_portions, int longest,
+                                        const int32_t *pages, int pages_ld, int page_size, int heads, int kv_rank, int rot_dim, float scale,
+                                        int window, int64_t stream) {
   if (n_portions <= 0 || longest <= 0) return 0;
-  if (heads <= 0 || !portions || !pages || page_size <= 0 || !mrs_seq_latent_attention_fits(kv_rank, rot_dim)) return -2;
+  if (heads <= 0 || (!portions && (!cu_tok || !past)) || !pages || page_size <= 0 || !mrs_seq_latent_attention_fits(kv_rank, rot_dim)) return -2;
   if ((q_ld | out_ld | cache_row) % 8 || (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15)) return -3;
   seql::Params p = {};
   p.q = (const __nv_bfloat16 *)q; p.cache = (const __nv_bfloat16 *)cache; p.o = (__nv_bfloat16 *)out;
   p.q_ld = q_ld; p.o_ld = out_ld; p.cache_row = cache_row;
-  p.portions = portions; p.pages = pages; p.pages_ld = pages_ld; p.page_size = page_size;
+  p.portions = portions; p.cu_tok = cu_tok; p.past = past; p.pages = pages; p.pages_ld = pages_ld; p.page_size = page_size;
   p.H = heads; p.DK = kv_rank + rot_dim; p.R = kv_rank;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   cudaStream_t st = (cudaStream_t)stream;
-  if (kv_rank <= 256) return seql::launch<4>(p, n_portions, longest, st);
-  if (kv_rank <= 512) return seql::launch<2>(p, n_portions, longest, st);
+  // row tiles per CTA: as many as the output columns allow, but no more than the longest portion fills (a decoded token's
+  // heads are one or two tiles: all eight warps then split its keys and columns)
+  const int64_t rows = (int64_t)longest * heads;
+  const int by_rank = kv_rank <= 256 ? 4 : (kv_rank <= 512 ? 2 : 1), by_rows = rows <= 16 ? 1 : (rows <= 32 ? 2 : 4);
+  const int mt = by_rank < by_rows ? by_rank : by_rows;
+  if (mt == 4) return seql::launch<4>(p, n_portions, longest, st);
+  if (mt == 2) return seql::launch<2>(p, n_portions, longest, st);
   return seql::launch<1>(p, n_portions, longest, st);
 }

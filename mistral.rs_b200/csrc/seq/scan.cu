@@ -74,6 +74,9 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
   T *rq = (T *)(rd + (VD ? TC * dkr : 0)), *rk = rq + TC * dkr, *rv = rk + TC * dkr;
   float *state = mode ? a.seg_state + ((int64_t)blockIdx.z * heads + h) * dk * dv : a.state + ((int64_t)a.slot[b] * heads + h) * dk * dv;
   float decay_product = 1.0f;
+  uint64_t dp2[VD ? RK / 2 : 1];      // per-row products of the decays over a segment (mode 1 with per-row decays)
+#pragma unroll
+  for (int r = 0; r < (VD ? RK / 2 : 1); r++) dp2[r] = pack2(1.0f, 1.0f);
 
   uint64_t S[RK / 2];      // the state column's rows as packed pairs (row 2i, row 2i + 1)
   if (mode == 2 || (mode == 0 && a.past[b] > 0)) {   // stage the tile [dk, cw] through shared memory so the global reads run along columns
@@ -221,8 +224,13 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
         for (int u = 0; u < 4; u++) {
           if (VD) {      // this row's own decay; a missing token keeps the state as it is
             const ulonglong2 d4 = *(const ulonglong2 *)(ds + (i0 + u) * dks + part * PS + r);
-            s01 = fma2(k4[u].x, bv2[u], mul2(lv[u] ? d4.x : av2[u], s01));
-            s23 = fma2(k4[u].y, bv2[u], mul2(lv[u] ? d4.y : av2[u], s23));
+            const uint64_t d01 = lv[u] ? d4.x : av2[u], d23 = lv[u] ? d4.y : av2[u];
+            s01 = fma2(k4[u].x, bv2[u], mul2(d01, s01));
+            s23 = fma2(k4[u].y, bv2[u], mul2(d23, s23));
+            if (mode == 1) {
+              dp2[VD ? r / 2 : 0] = mul2(dp2[VD ? r / 2 : 0], d01);
+              dp2[VD ? r / 2 + 1 : 0] = mul2(dp2[VD ? r / 2 + 1 : 0], d23);
+            }
           } else {
             s01 = fma2(k4[u].x, bv2[u], mul2(av2[u], s01));
             s23 = fma2(k4[u].y, bv2[u], mul2(av2[u], s23));
@@ -259,7 +267,18 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
       }
   }
   __syncthreads();
-  if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) a.seg_decay[(int64_t)blockIdx.z * heads + h] = decay_product;
+  if (VD) {
+    if (mode == 1 && blockIdx.x == 0 && cl == 0) {      // seg_decay holds one product per state row
+      float *out = a.seg_decay + ((int64_t)blockIdx.z * heads + h) * dk;
+#pragma unroll
+      for (int r = 0; r < RK; r += 2) {
+        float lo, hi;
+        unpack2(dp2[VD ? r / 2 : 0], lo, hi);
+        if (part * RK + r < dk) out[part * RK + r] = lo;
+        if (part * RK + r + 1 < dk) out[part * RK + r + 1] = hi;
+      }
+    }
+  } else if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) a.seg_decay[(int64_t)blockIdx.z * heads + h] = decay_product;
   if (mode != 2) {   // the state goes back the way it came
     float *tile = smem;
 #pragma unroll
@@ -291,7 +310,7 @@ __global__ void scan_chain_kernel(const mrs_seq_scan_args a) {
     float *p = a.seg_state + (z * a.heads + h) * per + e;
     const float local = *p;
     *p = run;
-    run = fmaf(a.seg_decay[z * a.heads + h], run, local);
+    run = fmaf(a.decay_vec ? a.seg_decay[(z * a.heads + h) * a.dk + e / a.dv] : a.seg_decay[z * a.heads + h], run, local);
   }
   *slot_state = run;
 }
@@ -321,7 +340,7 @@ static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     allowed = bytes;
   }
-  if (!VD && a.n_segs > 1 && a.seg_state && a.seg_decay && a.seg_len > 0) {   // per-row decays run every portion in one pass
+  if (a.n_segs > 1 && a.seg_state && a.seg_decay && a.seg_len > 0) {
     dim3 grid((a.dv + cw - 1) / cw, a.heads, a.n_seq * a.n_segs);
     kern<<<grid, cw * parts, bytes, st>>>(a, parts, cw, aligned ? 1 : 0, 1);
     const int per = a.dk * a.dv;
@@ -356,6 +375,34 @@ __global__ void causal_conv_kernel(const T *__restrict__ in, int64_t in_ld, int 
     acc = fmaf(taps[(int64_t)c * n_taps + j], x, acc);
   }
   out[(int64_t)t * channels + c] = from_f32<T>(apply_act(acc, act));
+}
+
+// four neighbouring channels per thread (16-byte accesses) when rows and channel counts are 4-element aligned
+template <typename T>
+__global__ void causal_conv_vec_kernel(const T *__restrict__ in, int64_t in_ld, int col0, const float *__restrict__ taps,
+                                       const float *__restrict__ bias, int channels, int n_taps, int act,
+                                       const float *__restrict__ conv_state, const int32_t *__restrict__ cu_tok,
+                                       const int32_t *__restrict__ past, const int32_t *__restrict__ slot,
+                                       const int32_t *__restrict__ seq_of_tok, T *__restrict__ out) {
+  const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= channels) return;
+  const int s = seq_of_tok[t], first = cu_tok[s], i = t - first, carried = n_taps - 1;
+  const bool has_past = past[s] > 0;
+  const float *st = conv_state + (int64_t)slot[s] * carried * channels;
+  float4 acc = bias ? *(const float4 *)(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  const float *w = taps + (int64_t)c * n_taps;
+  for (int j = 0; j < n_taps; j++) {
+    const int src = i - carried + j;
+    float4 x;
+    if (src >= 0) x = load4<T>(in + (int64_t)(first + src) * in_ld + col0 + c);
+    else if (has_past) x = *(const float4 *)(st + (int64_t)(carried + src) * channels + c);
+    else x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    acc.x = fmaf(w[j], x.x, acc.x);
+    acc.y = fmaf(w[n_taps + j], x.y, acc.y);
+    acc.z = fmaf(w[2 * n_taps + j], x.z, acc.z);
+    acc.w = fmaf(w[3 * n_taps + j], x.w, acc.w);
+  }
+  store4<T>(out + (int64_t)t * channels + c, act4(acc, act));
 }
 
 // runs after the convolution: the carried inputs become the last n_taps-1 inputs of the sequence
@@ -444,6 +491,47 @@ __global__ void __launch_bounds__(1024) gated_group_norm_kernel(const float *__r
   }
 }
 
+// narrow groups (a head's value size): one warp per (token, group), the group's row in registers, eight groups per CTA
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_norm_warp_kernel(const float *__restrict__ x, const T *__restrict__ gate, int64_t gate_ld,
+                                                                    const float *__restrict__ weight, T *__restrict__ out, int64_t out_ld,
+                                                                    float out_scale, int cols, int groups, float eps, int gate_act, int gate_first,
+                                                                    int64_t n_jobs) {
+  constexpr int KEEP = 8;
+  const int lane = threadIdx.x & 31;
+  const int64_t job = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (job >= n_jobs) return;
+  const int64_t t = job / groups;
+  const int gr = (int)(job % groups), n = cols / groups, c0 = gr * n;
+  const float *xr = x + t * cols + c0;
+  const T *gp = gate ? gate + t * gate_ld + c0 : nullptr;
+  T *dst = out + t * out_ld + c0;
+  const float *w = weight + c0;
+  float4 xv[KEEP], gv[KEEP];
+  float ss = 0.0f;
+#pragma unroll
+  for (int it = 0; it < KEEP; it++) {
+    const int c = (it * 32 + lane) * 4;
+    if (c < n) {
+      xv[it] = *(const float4 *)(xr + c);
+      gv[it] = gp ? act4(load4<T>(gp + c), gate_act) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+      if (gate_first) xv[it] = make_float4(xv[it].x * gv[it].x, xv[it].y * gv[it].y, xv[it].z * gv[it].z, xv[it].w * gv[it].w);
+      ss += xv[it].x * xv[it].x + xv[it].y * xv[it].y + xv[it].z * xv[it].z + xv[it].w * xv[it].w;
+    }
+  }
+  const float inv = rsqrtf_exact(warp_sum(ss) / (float)n + eps);
+#pragma unroll
+  for (int it = 0; it < KEEP; it++) {
+    const int c = (it * 32 + lane) * 4;
+    if (c < n) {
+      const float4 ww = *(const float4 *)(w + c);
+      float4 r = make_float4(xv[it].x * inv * ww.x, xv[it].y * inv * ww.y, xv[it].z * inv * ww.z, xv[it].w * inv * ww.w);
+      if (!gate_first) r = make_float4(r.x * gv[it].x, r.y * gv[it].y, r.z * gv[it].z, r.w * gv[it].w);
+      store4<T>(dst + c, make_float4(r.x * out_scale, r.y * out_scale, r.z * out_scale, r.w * out_scale));
+    }
+  }
+}
+
 template <typename T>
 __global__ void activate_cols_kernel(T *__restrict__ x, int64_t ld, int cols, int act, int vec) {
   T *row = x + (int64_t)blockIdx.x * ld;
@@ -502,10 +590,17 @@ extern "C" int mrs_seq_causal_conv(const void *in, int64_t in_ld, int col0, int 
   if (n_taps < 1 || channels < 1) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   const int th = 128;
+  const bool vec = channels % 4 == 0 && in_ld % 4 == 0 && col0 % 4 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                   (uintptr_t)conv_state % 16 == 0 && (uintptr_t)bias % 16 == 0;
   SEQ_DISPATCH_DTYPE(dtype, {
-    causal_conv_kernel<T><<<dim3(n_tok, (channels + th - 1) / th), th, 0, st>>>((const T *)in, in_ld, col0, taps, bias, channels,
-                                                                               n_taps, act, conv_state, cu_tok, past, slot,
-                                                                               seq_of_tok, (T *)out);
+    if (vec)
+      causal_conv_vec_kernel<T><<<dim3(n_tok, (channels / 4 + th - 1) / th), th, 0, st>>>((const T *)in, in_ld, col0, taps, bias, channels,
+                                                                                         n_taps, act, conv_state, cu_tok, past, slot,
+                                                                                         seq_of_tok, (T *)out);
+    else
+      causal_conv_kernel<T><<<dim3(n_tok, (channels + th - 1) / th), th, 0, st>>>((const T *)in, in_ld, col0, taps, bias, channels,
+                                                                                 n_taps, act, conv_state, cu_tok, past, slot,
+                                                                                 seq_of_tok, (T *)out);
     if (n_taps > 1)
       conv_state_advance_kernel<T><<<dim3((channels + th - 1) / th, n_seq), th, 0, st>>>((const T *)in, in_ld, col0, channels,
                                                                                         n_taps, conv_state, cu_tok, past, slot);
@@ -531,6 +626,12 @@ extern "C" int mrs_seq_gated_group_norm(const float *x, const void *gate, int64_
   const bool vec = n % 4 == 0 && gate_ld % 4 == 0 && out_ld % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)gate % 16 == 0 &&
                    (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0 && n <= 4 * 1024 * 4;
   cudaStream_t st = (cudaStream_t)stream;
+  if (vec && n <= 1024 && (int64_t)n_tok * groups >= 1024) {
+    const int64_t jobs = (int64_t)n_tok * groups;
+    SEQ_DISPATCH_DTYPE(dtype, (gated_group_norm_warp_kernel<T><<<(unsigned)((jobs + 7) / 8), 256, 0, st>>>(
+                                  x, (const T *)gate, gate_ld, weight, (T *)out, out_ld, out_scale, cols, groups, eps, gate_act, gate_first, jobs)));
+    return launch_status();
+  }
   if (vec) {
     const int items = n / 4;                                    // vector items per row
     int th = 64;

@@ -175,8 +175,9 @@ class LatentAttentionMixer:
 
     Computed in the absorbed form: a head's query becomes [W_uk,h^T q_plain | q_rot] (size kv_rank + dr), attention runs
     over the cached rows as one key/value head whose values are the rows' first kv_rank columns, and W_uv,h maps the
-    result to the head's output.  Long portions (32 tokens or more, bf16) run on the tensor-core latent kernel, every other
-    token on the (token, head) kernel over the pages.  `shares`: this mixer has no W_dkv and reads the cache another layer fills."""
+    result to the head's output.  In bf16 every sequence of a step, a prompt portion or a single decoded token, runs on the
+    tensor-core latent kernel (all heads of a token share one fetched key tile); f32, and sizes the kernel does not take,
+    run on the (token, head) kernel over the pages.  `shares`: this mixer has no W_dkv and reads the cache another layer fills."""
 
     def __init__(self, w_down, w_uq, w_uk, w_uv, w_o, q_norm_w, kv_norm_w, heads, dn, dr, dv, q_rank, kv_rank, scale, window, rotation, eps,
                  page_size, shares=False):
@@ -207,12 +208,10 @@ class LatentAttentionMixer:
         torch.bmm(q[:, :, :dn].transpose(0, 1), self.w_uk, out=qa[:, :, :R].transpose(0, 1))
         K.rotate_pairs(q.view(T, -1), dn, dn + dr, qa.view(T, -1), R, self.row, H, dr, rot_dims, cos_sin)
         o = torch.empty(T, H, R, dtype=h.dtype, device=h.device)
-        tok_index = None
-        if batch.long and h.dtype == torch.bfloat16 and K.latent_attention_fits(R, dr) and latent.stride(0) % 8 == 0:
+        if h.dtype == torch.bfloat16 and K.latent_attention_fits(R, dr) and latent.stride(0) % 8 == 0:
             K.latent_prompt_attention(qa.view(T, -1), latent, H, R, dr, self.scale, self.window, batch, self.page_size, o.view(T, -1))
-            tok_index = batch.short_tok            # long portions ran on tensor cores; the rest goes token by token
-        if tok_index is None or tok_index.numel():
-            K.latent_attention(qa.view(T, -1), latent, H, R, dr, self.scale, self.window, batch, self.page_size, o.view(T, -1), tok_index)
+        else:
+            K.latent_attention(qa.view(T, -1), latent, H, R, dr, self.scale, self.window, batch, self.page_size, o.view(T, -1))
         out = torch.empty(T, H, self.dv, dtype=h.dtype, device=h.device)
         torch.bmm(o.transpose(0, 1), self.w_uv_t, out=out.transpose(0, 1))
         return linear(out.view(T, H * self.dv), self.w_o)

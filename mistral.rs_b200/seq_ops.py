@@ -238,14 +238,14 @@ def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, b
     a.cu_tok, a.past, a.slot = batch.cu_tok.data_ptr(), batch.past.data_ptr(), batch.slot.data_ptr()
     a.n_seq, a.n_tok, a.out = batch.n_seq, T, out.data_ptr()
     longest = getattr(batch, "longest", 0)
-    if longest >= SCAN_SEGMENT_MIN_TOKENS and decay_vec is None:
+    if longest >= SCAN_SEGMENT_MIN_TOKENS:
         seg = SCAN_SEGMENT
         while batch.n_seq * -(-longest // seg) * heads * dk * dv * 4 > SCAN_SCRATCH_BYTES:
             seg *= 2
         n_segs = -(-longest // seg)
         if n_segs > 1:
             seg_state = torch.empty(batch.n_seq * n_segs * heads * dk * dv, dtype=torch.float32, device=q.device)
-            seg_decay = torch.empty(batch.n_seq * n_segs * heads, dtype=torch.float32, device=q.device)
+            seg_decay = torch.empty(batch.n_seq * n_segs * heads * (dk if decay_vec is not None else 1), dtype=torch.float32, device=q.device)
             a.seg_state, a.seg_decay, a.seg_len, a.n_segs = seg_state.data_ptr(), seg_decay.data_ptr(), seg, n_segs
     _ok(lib().mrs_seq_linear_scan(ctypes.byref(a), _st(q)), "linear_scan")
     return out
@@ -524,9 +524,10 @@ def latent_attention_fits(kv_rank, rot_dim):
 
 
 def latent_prompt_attention(qa, latent, heads, kv_rank, rot_dim, scale, window, batch, page_size, out):
-    """The long portions of the step (batch.long) of the absorbed latent attention on tensor cores."""
+    """Absorbed latent attention of every sequence of the step on tensor cores: prompt portions of any length and single
+    decoded tokens alike (a token's heads are rows of one tile; the window's latents are fetched once for all of them)."""
     _ok(lib().mrs_seq_latent_attention(_p(qa), _l(qa.stride(0)), _p(latent), _l(latent.stride(0)), _p(out), _l(out.stride(0)),
-                                       _p(batch.long_rows), _i(len(batch.long)), _i(max(n for _, n, _, _ in batch.long)), _p(batch.pages),
+                                       _p(None), _p(batch.cu_tok), _p(batch.past), _i(batch.n_seq), _i(batch.longest), _p(batch.pages),
                                        _i(batch.pages.shape[1]), _i(page_size), _i(heads), _i(kv_rank), _i(rot_dim), _f(scale), _i(int(window)),
                                        _st(qa)), "latent_attention")
 

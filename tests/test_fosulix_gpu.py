@@ -390,9 +390,19 @@ def test_tied_gate_other_sizes(cuda, layer):
 
 
 def test_tied_gate_long_portion(cuda):
-    """A portion long enough for other recurrences to be scanned in segments runs in one pass here, after a state carried in."""
+    """A portion long enough to be scanned in segments, after a state carried in."""
     got, want = mixer_case(cuda, gate_layer(heads=2, dim=16, vdim=16), torch.float32, 1300, [100, 1200])
     close_rows(got, want, 5e-5)
+
+
+def test_tied_gate_scan_in_segments(cuda, monkeypatch):
+    """Long portions are scanned as segments side by side, every state row with its own product of decays: made to happen on
+    short portions here, with ragged last segments and a state carried in from an earlier portion."""
+    monkeypatch.setattr(K, "SCAN_SEGMENT", 16)
+    monkeypatch.setattr(K, "SCAN_SEGMENT_MIN_TOKENS", 40)
+    for layer in (gate_layer(), gate_layer(heads=2, dim=136, vdim=24), gate_layer(heads=1, dim=7, vdim=5)):
+        got, want = mixer_case(cuda, layer, torch.float32, 150, [70, 3, 77])
+        close_rows(got, want, 5e-5)
 
 
 def test_first_token_survives_far(cuda):
