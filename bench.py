@@ -913,7 +913,7 @@ def bench_fosulix(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
                                 "like_hbm_frac": gbs(8 * T * W * (4 + 4 + 2 + 2) - T * W * 2, kops.get("residual_tanh_norm"))}
         roof["causal_conv"] = {"ms": ops.get("causal_conv"), "hbm_frac": gbs(4 * T * W * (2 + 2), ops.get("causal_conv")), "like": "none (Kilizen has no convolution)"}
         # latent preparation: the projection's latent columns read, query latent written, latent row written; then the rotated query parts
-        prep = T * 2 * (2 * qr + R + dr) + T * 2 * (R + dr) + T * 2 * 2 * qr + 2 * T * H * dr * 2 * 2
+        prep = T * 2 * (2 * qr + R + dr) + T * 2 * (R + dr) + 2 * T * 2 * qr + 2 * T * H * dr * 2 * 2      # both latent layers
         G = max(1, H // 4)
         roof["latent_prepare + rotate_pairs"] = {"ms": ops.get("latent_prepare", 0.0) + ops.get("rotate_pairs", 0.0),
                                                  "hbm_frac": gbs(prep, ops.get("latent_prepare", 0.0) + ops.get("rotate_pairs", 0.0)), "like": "attention_prepare",
@@ -943,9 +943,9 @@ def bench_fosulix(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
             # per token and layer the window's latent rows are read once whatever the head count (they sit in L2 for the other heads)
             lbytes = 2 * b * min(ctx, win) * (R + dr) * 2
             kbytes = b * (2 * G * d * 2 * ctx + 2 * G * d * 2 * min(ctx, kwin))
-            roof["paged_attention (decode, b=%d)" % b] = {"ms": dk[0].get("paged_attention"), "hbm_frac": gbs(lbytes, dk[0].get("paged_attention")),
-                                                          "like": "paged_attention", "like_ms": dk[1].get("paged_attention"),
-                                                          "like_hbm_frac": gbs(kbytes, dk[1].get("paged_attention"))}
+            roof["latent_prompt_attention (decode, b=%d)" % b] = {"ms": dk[0].get("latent_prompt_attention"), "hbm_frac": gbs(lbytes, dk[0].get("latent_prompt_attention")),
+                                                                  "like": "paged_attention", "like_ms": dk[1].get("paged_attention"),
+                                                                  "like_hbm_frac": gbs(kbytes, dk[1].get("paged_attention"))}
         row["roofline"] = roof
         out["sizes"].append(row)
     out["value"] = out["sizes"][0]["prefill_tok_s"]
