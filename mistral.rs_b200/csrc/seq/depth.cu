@@ -20,7 +20,7 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(1024) rms_residual_kernel(const mrs_seq_rms_residual_args a) {
   extern __shared__ __align__(16) float row[];   // [width]
   __shared__ float red[33];
-  __shared__ float mix[64];
+  __shared__ float mix[128];
   const int t = blockIdx.x, width = a.width;
   const int64_t at = (int64_t)t * width;
   const T *y = (const T *)a.y;
@@ -103,7 +103,7 @@ extern "C" int mrs_seq_embed_scaled(const void *table, int dtype, const int32_t 
 extern "C" int mrs_seq_rms_residual(const mrs_seq_rms_residual_args *args, int64_t stream) {
   const mrs_seq_rms_residual_args &a = *args;
   if (a.n_tok <= 0) return 0;
-  if (!a.src || a.width <= 0 || (a.hist && (a.n_hist < 1 || a.n_hist > 64 || !a.mix)) || (a.next_out && !a.next_w)) return -2;
+  if (!a.src || a.width <= 0 || (a.hist && (a.n_hist < 1 || a.n_hist > 128 || !a.mix)) || (a.next_out && !a.next_w)) return -2;
   const size_t bytes = (size_t)a.width * sizeof(float);
   if (bytes > 200 * 1024) return -2;
   auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
