@@ -377,32 +377,62 @@ __global__ void causal_conv_kernel(const T *__restrict__ in, int64_t in_ld, int 
   out[(int64_t)t * channels + c] = from_f32<T>(apply_act(acc, act));
 }
 
-// four neighbouring channels per thread (16-byte accesses) when rows and channel counts are 4-element aligned
+// Four neighbouring channels per thread (16-byte accesses) and CONV_TB neighbouring tokens per CTA, when rows and channel
+// counts are 4-element aligned and there are at most 8 taps: the thread walks its tokens with the last n_taps - 1 inputs in
+// registers, so every input is loaded once (not once per tap) and the index chain token -> sequence -> first row / slot is
+// followed once per CTA (and again where a new sequence starts inside the block), not once per output.
+constexpr int CONV_TB = 16, CONV_MAXC = 7;
 template <typename T>
-__global__ void causal_conv_vec_kernel(const T *__restrict__ in, int64_t in_ld, int col0, const float *__restrict__ taps,
+__global__ void __launch_bounds__(128) causal_conv_vec_kernel(const T *__restrict__ in, int64_t in_ld, int col0, const float *__restrict__ taps,
                                        const float *__restrict__ bias, int channels, int n_taps, int act,
                                        const float *__restrict__ conv_state, const int32_t *__restrict__ cu_tok,
                                        const int32_t *__restrict__ past, const int32_t *__restrict__ slot,
-                                       const int32_t *__restrict__ seq_of_tok, T *__restrict__ out) {
-  const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+                                       const int32_t *__restrict__ seq_of_tok, int n_tok, T *__restrict__ out) {
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   if (c >= channels) return;
-  const int s = seq_of_tok[t], first = cu_tok[s], i = t - first, carried = n_taps - 1;
-  const bool has_past = past[s] > 0;
-  const float *st = conv_state + (int64_t)slot[s] * carried * channels;
-  float4 acc = bias ? *(const float4 *)(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  const float *w = taps + (int64_t)c * n_taps;
-  for (int j = 0; j < n_taps; j++) {
-    const int src = i - carried + j;
-    float4 x;
-    if (src >= 0) x = load4<T>(in + (int64_t)(first + src) * in_ld + col0 + c);
-    else if (has_past) x = *(const float4 *)(st + (int64_t)(carried + src) * channels + c);
-    else x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    acc.x = fmaf(w[j], x.x, acc.x);
-    acc.y = fmaf(w[n_taps + j], x.y, acc.y);
-    acc.z = fmaf(w[2 * n_taps + j], x.z, acc.z);
-    acc.w = fmaf(w[3 * n_taps + j], x.w, acc.w);
+  const int t0 = blockIdx.x * CONV_TB, t1 = min(n_tok, t0 + CONV_TB), carried = n_taps - 1, lead = CONV_MAXC - carried;
+  float w[4][CONV_MAXC + 1];       // taps right-aligned: w[.][lead + j] = tap j
+#pragma unroll
+  for (int k = 0; k <= CONV_MAXC; k++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) w[e][k] = k >= lead ? taps[(int64_t)(c + e) * n_taps + k - lead] : 0.0f;
+  const float4 b4 = bias ? *(const float4 *)(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float4 hist[CONV_MAXC];          // hist[CONV_MAXC - 1] = the input before the current token
+  int s = -1;
+  for (int t = t0; t < t1; t++) {
+    const int st = seq_of_tok[t];
+    if (st != s) {                 // the block's first token, or a sequence starts here: fetch the inputs before it
+      s = st;
+      const int first = cu_tok[s], i = t - first;
+      const bool has_past = past[s] > 0;
+      const float *cs = conv_state + (int64_t)slot[s] * carried * channels;
+#pragma unroll
+      for (int k = 0; k < CONV_MAXC; k++) {
+        const int src = i - CONV_MAXC + k;            // k >= lead: the carried range
+        if (k < lead) hist[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        else if (src >= 0) hist[k] = load4<T>(in + (int64_t)(first + src) * in_ld + col0 + c);
+        else if (has_past) hist[k] = *(const float4 *)(cs + (int64_t)(carried + src) * channels + c);
+        else hist[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    }
+    const float4 x = load4<T>(in + (int64_t)t * in_ld + col0 + c);
+    float4 acc = b4;
+#pragma unroll
+    for (int k = 0; k < CONV_MAXC; k++) {
+      acc.x = fmaf(w[0][k], hist[k].x, acc.x);
+      acc.y = fmaf(w[1][k], hist[k].y, acc.y);
+      acc.z = fmaf(w[2][k], hist[k].z, acc.z);
+      acc.w = fmaf(w[3][k], hist[k].w, acc.w);
+    }
+    acc.x = fmaf(w[0][CONV_MAXC], x.x, acc.x);
+    acc.y = fmaf(w[1][CONV_MAXC], x.y, acc.y);
+    acc.z = fmaf(w[2][CONV_MAXC], x.z, acc.z);
+    acc.w = fmaf(w[3][CONV_MAXC], x.w, acc.w);
+    store4<T>(out + (int64_t)t * channels + c, act4(acc, act));
+#pragma unroll
+    for (int k = 0; k + 1 < CONV_MAXC; k++) hist[k] = hist[k + 1];
+    hist[CONV_MAXC - 1] = x;
   }
-  store4<T>(out + (int64_t)t * channels + c, act4(acc, act));
 }
 
 // runs after the convolution: the carried inputs become the last n_taps-1 inputs of the sequence
@@ -591,12 +621,11 @@ extern "C" int mrs_seq_causal_conv(const void *in, int64_t in_ld, int col0, int 
   cudaStream_t st = (cudaStream_t)stream;
   const int th = 128;
   const bool vec = channels % 4 == 0 && in_ld % 4 == 0 && col0 % 4 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0 &&
-                   (uintptr_t)conv_state % 16 == 0 && (uintptr_t)bias % 16 == 0;
+                   (uintptr_t)conv_state % 16 == 0 && (uintptr_t)bias % 16 == 0 && n_taps <= CONV_MAXC + 1;
   SEQ_DISPATCH_DTYPE(dtype, {
     if (vec)
-      causal_conv_vec_kernel<T><<<dim3(n_tok, (channels / 4 + th - 1) / th), th, 0, st>>>((const T *)in, in_ld, col0, taps, bias, channels,
-                                                                                         n_taps, act, conv_state, cu_tok, past, slot,
-                                                                                         seq_of_tok, (T *)out);
+      causal_conv_vec_kernel<T><<<dim3((n_tok + CONV_TB - 1) / CONV_TB, (channels / 4 + th - 1) / th), th, 0, st>>>(
+          (const T *)in, in_ld, col0, taps, bias, channels, n_taps, act, conv_state, cu_tok, past, slot, seq_of_tok, n_tok, (T *)out);
     else
       causal_conv_kernel<T><<<dim3(n_tok, (channels + th - 1) / th), th, 0, st>>>((const T *)in, in_ld, col0, taps, bias, channels,
                                                                                  n_taps, act, conv_state, cu_tok, past, slot,

@@ -209,7 +209,7 @@ def test_latent_attention_other_sizes(cuda, layer):
     close_rows(got, want, 3e-5)
 
 
-TC_LAYERS = [latent_layer(heads=6, dim=32, rot_dim=32, vdim=40, q_rank=64, kv_rank=96, window=72),
+TC_LAYERS = [latent_layer(heads=7, dim=32, rot_dim=24, vdim=40, q_rank=64, kv_rank=104, window=75),
              latent_layer(heads=16, dim=16, rot_dim=16, vdim=24, q_rank=32, kv_rank=264, window=100),
              latent_layer(heads=5, dim=16, rot_dim=8, vdim=16, q_rank=32, kv_rank=520, window=4096),
              latent_layer(heads=3, window=64), latent_layer(heads=1, dim=8, rot_dim=8, vdim=8, q_rank=8, kv_rank=8, window=33)]
