@@ -1,7 +1,9 @@
 /* mrs_b200_seq.h — C ABI of the sequence-mixer kernels (libmrs_b200_seq.so): multi-stream residuals
- * (hyper-connections), gated linear recurrences with a per-sequence f32 state (linear attention with decay,
- * selective state spaces), short causal convolutions, windowed attention over a paged cache with unequal key
- * and value head sizes, grouped-limited expert routing and the expert feed-forward.
+ * (hyper-connections), single residuals with Dynamic Tanh or RMS norms (the latter with a depth-weighted average over
+ * the layers' results), gated linear recurrences with a per-sequence f32 state (linear attention with decay, selective
+ * state spaces, matrix memories, per-row forget gates that also write), short causal convolutions, windowed attention
+ * over a paged cache with unequal key and value head sizes, attention over cached low-rank latents, grouped-limited
+ * expert routing and the expert feed-forward.
  *
  * Conventions: raw device pointers, caller-owned memory, stream-ordered, no allocation and no host
  * synchronisation; every function returns 0 or a cudaError (negative: a bad argument).  `dtype` is the storage

@@ -114,10 +114,10 @@ class FosulixModel:
         self.embed, self.final_norm = mat("embed"), vec("final.norm")
         self.layers, rotations = [], {}
 
-        def rotation(rot):
+        def rotation(rot, rot_dim):
             if not rot:
                 return None
-            r = M.Rotation(rot["dims"], rot["base"], rot.get("scaling"), device)
+            r = M.Rotation(rot.get("dims", rot_dim), rot["base"], rot.get("scaling"), device)
             return rotations.setdefault(r.key, r)          # layers with equal constants share one table per step
 
         for i, L in enumerate(cfg.layers):
@@ -138,7 +138,7 @@ class FosulixModel:
                 lay.mixer = M.LatentAttentionMixer(w_down, mat(p + "mix.uq"), mat(p + "mix.uk"), mat(p + "mix.uv"), mat(p + "mix.o"),
                                                    vec(p + "mix.dq.norm"), None if shares else vec(p + "mix.dkv.norm"), H, dk, int(m["rot_dim"]), dv,
                                                    int(m["q_rank"]), int(m["kv_rank"]), float(m["scale"]), int((m.get("mask") or {}).get("size", 0)),
-                                                   rotation(m.get("rot")), cfg.eps, page_size, shares=shares)
+                                                   rotation(m.get("rot"), int(m["rot_dim"])), cfg.eps, page_size, shares=shares)
             mlp, lay.mlp = L.get("mlp"), None
             if mlp is not None:
                 lay.norm2 = vec(p + "norm2")
