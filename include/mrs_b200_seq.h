@@ -63,8 +63,18 @@ int mrs_seq_residual_tanh_norm(float *x, const void *y, int dtype, const float *
 /* out[t][:] = table[ids[t]][:] * scale (f32). */
 int mrs_seq_embed_scaled(const void *table, int dtype, const int32_t *ids, float scale, float *out, int n_tok, int width,
                          int64_t stream);
+/* out[t][:] = table[ids[t]][:] * scale + pairs[row][:] (f32): a token embedding plus a hashed embedding of the (previous
+ * token, token) pair, row = (previous * mul_prev + token * mul_cur) mod buckets, or row `buckets` (the table's last) for a
+ * sequence's first token.  The previous token of a portion's first token comes from prev_state[slot] (int32 per state slot),
+ * which is then set to the portion's last token.  cu_tok / past / slot / seq_of_tok describe the step's sequences. */
+int mrs_seq_embed_pair(const void *table, const void *pairs, int dtype, const int32_t *ids, float scale, int64_t buckets,
+                       int64_t mul_prev, int64_t mul_cur, int32_t *prev_state, const int32_t *cu_tok, const int32_t *past,
+                       const int32_t *slot, const int32_t *seq_of_tok, float *out, int n_tok, int width, int64_t stream);
 /* One pass per token over an f32 residual, every part optional (NULL: skipped), in this order:
- *   v = src[t] + mult * y[t]                       (y: a sublayer's output, activation type; NULL: v = src[t])
+ *   v = src[t] + mult * y[t]                       (y: a sublayer's output, activation type; NULL: v = src[t]; with post_w, y[t]
+ *                                                    is first RMS-normed: y / sqrt(mean(y^2) + eps) * post_w — a norm after the
+ *                                                    sublayer as well as before it)
+ *   v += add_vec                                    (f32 [width], the same for every token; NULL: nothing)
  *   dst[t] = v                                      (dst may be src)
  *   v = sum_(j < n_hist) mix[j] * hist[j][t]        (hist f32 [n_hist][n_tok][width] with entry stride hist_stride floats;
  *                                                    an entry may be dst, which then already holds this token's v)
@@ -86,6 +96,8 @@ typedef struct {
   float eps;
   void *next_out;
   int dtype, n_tok, width;
+  const float *post_w;
+  const float *add_vec;
 } mrs_seq_rms_residual_args;
 int mrs_seq_rms_residual(const mrs_seq_rms_residual_args *args, int64_t stream);
 
@@ -100,6 +112,10 @@ int mrs_seq_glu_join(const void *x, void *out, int dtype, int n_tok, int half, c
  * columns of an activation tensor (row stride raw_ld); gate f32 [n_tok, cols]. */
 int mrs_seq_bounded_gate(const void *raw, int64_t raw_ld, int dtype, const float *bias, const float *lower, int n_tok, int cols,
                          float *gate, int64_t stream);
+/* gate[t][c] = sigmoid(raw[t][c] + bias[c])^power in f32, as exp(power * log_sigmoid(.)): a decay per channel whose
+ * logarithm is a softened log-sigmoid (power = 1 / temperature). */
+int mrs_seq_power_gate(const void *raw, int64_t raw_ld, int dtype, const float *bias, float power, int n_tok, int cols, float *gate,
+                       int64_t stream);
 /* Root-mean-square norm of f32 rows in `groups` equal parts, times weight, with a gate read from an activation
  * tensor (row stride gate_ld): gate_first != 0: norm(x * act(gate)) * w; else norm(x) * w * act(gate).  The result,
  * times out_scale, goes to out[t * out_ld + c]. */
@@ -124,9 +140,10 @@ int mrs_seq_ssm_steps(const void *in, int64_t in_ld, int col0, int dtype, const 
  *   S_t = a_t S_(t-1) + b_t k_t v_t^T     (S f32 [dk, dv], kept in state[slot][h])
  *   o_t = S_t^T q_t + skip[h] v_t         (o f32 [n_tok, heads * dv])
  * a_t = decay_tok[t][h] (or decay_head[h] when decay_tok is NULL), b_t = scale_tok[t][h] (1 when NULL), skip NULL: 0.
- * decay_vec f32 [n_tok, heads, dk] (then decay_tok, decay_head and k are NULL and qk_groups == heads): every state row has
- * its own decay and the key is its complement, S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; seg_decay then holds one product
- * per state row, f32 [n_seq * n_segs, heads, dk].
+ * decay_vec f32 [n_tok, heads, dk] (then decay_tok and decay_head are NULL and qk_groups == heads): every state row has its
+ * own decay, S_t = diag(f_t) S_(t-1) + k_t v_t^T; with k NULL the key is the decay's complement, S_t = diag(f_t) S_(t-1) +
+ * (1 - f_t) v_t^T; seg_decay then holds one product per state row, f32 [n_seq * n_segs, heads, dk].
+ * q_scale: a constant factor on the queries, applied in f32 as they are read (0: none).
  * q, k: [n_tok, qk_groups, dk] with row strides q_ld / k_ld; v: [n_tok, heads, dv] with row stride v_ld; `act` is
  * applied to q, k and v as they are read.
  * Long portions can run as n_segs segments of seg_len tokens side by side (n_segs > 1): the caller provides
@@ -146,6 +163,7 @@ typedef struct {
   float *seg_state, *seg_decay;
   int seg_len, n_segs;
   const float *decay_vec;
+  float q_scale;
 } mrs_seq_scan_args;
 int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream);
 
@@ -226,8 +244,30 @@ typedef struct {
   float out_scale;
   int64_t k_row, v_row;   /* elements between the cache rows of neighbouring slots; 0: kv_heads * dk / kv_heads * dv.  Values that
                              are a column range of the key rows: v_cache = k_cache + first column, v_row = k_row. */
+  int pool;               /* > 0 (needs window > 0, keep_first 0): besides its window a position sees one averaged key / value per
+                             block of `pool` positions that lies wholly before the window (mrs_seq_pool_blocks makes them) */
+  int64_t pool_base;      /* cache row of the first averaged entry: block b of a sequence sits at row
+                             pool_base + page * ceil(page_size / pool) + (b - first block that starts in the page) */
+  int v_shared;           /* != 0: every head reads value columns [0, dv) of a row, whatever its key/value head — with dv = all
+                             value heads side by side, head h's weights are applied to every value head */
+  int out_f32;            /* != 0: out is f32 whatever the activation type */
 } mrs_seq_paged_attention_args;
 int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args, int64_t stream);
+/* Averaged cache entries for attention over pooled blocks: for every token of the step whose position ends a block of `pool`
+ * positions, the mean (f32 sum / pool) of the block's cached rows is written to the block's row (see pool_base above), in the
+ * k cache over k_cols columns and in the v cache over v_cols columns.  Run after the step's keys and values are stored. */
+int mrs_seq_pool_blocks(void *k_cache, void *v_cache, int dtype, int64_t k_row, int64_t v_row, int k_cols, int v_cols, int pool,
+                        int64_t pool_base, const int32_t *pages, int pages_ld, int page_size, const int32_t *seq_of_tok,
+                        const int32_t *pos_of_tok, int n_tok, int64_t stream);
+/* Attention weights mixed across heads after the softmax, applied through linearity: a f32 [n_tok, heads, kv_heads * dv]
+ * holds, per head g, its weights applied to EVERY value head (mrs_seq_paged_attention with v_shared); out[t][h][:] =
+ * act(gate[t][h][:]) * sum_g mix[h][g] * a[t][g][value head of h][:].  mix f32 [heads, heads]; gate: activation type, row
+ * stride gate_ld, NULL: none. */
+int mrs_seq_mix_heads(const float *a, const float *mix, const void *gate, int64_t gate_ld, int gate_act, void *out, int64_t out_ld,
+                      int dtype, int heads, int kv_heads, int dv, int n_tok, int64_t stream);
+/* x[t][c] *= act(gate[t][c / group]) for c < cols: a gate per entry (group 1) or per head (group = head size). */
+int mrs_seq_gate_cols(void *x, int64_t x_ld, const void *gate, int64_t gate_ld, int dtype, int cols, int group, int act, int n_tok,
+                      int64_t stream);
 /* The long portions of a step on tensor cores (bf16, dk = dv = d of 64 or 128, q / out rows 16-byte aligned), with the same
  * window / keep_first / sink rule: queries are the portion's fresh rows of q, keys and values are read from the pages (the
  * portion's own, stored by the preparation, and everything cached before).  portions [n][4]: first row inside q / out,

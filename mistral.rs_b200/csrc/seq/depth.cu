@@ -16,6 +16,30 @@ __global__ void embed_scaled_kernel(const T *__restrict__ table, const int32_t *
   for (int c = threadIdx.x; c < width; c += blockDim.x) out[(int64_t)t * width + c] = to_f32<T>(row[c]) * scale;
 }
 
+// One CTA per token: the token's embedding row times a scale plus a row of the pair table chosen by a hash of (previous
+// token, token).  Inside a portion the previous token is the row before; a portion's first token takes it from the
+// sequence's state slot, and that same CTA then leaves the portion's last token there (one reader and writer per slot).
+template <typename T>
+__global__ void embed_pair_kernel(const T *__restrict__ table, const T *__restrict__ pairs, const int32_t *__restrict__ ids, float scale,
+                                  int64_t buckets, int64_t mul_prev, int64_t mul_cur, int32_t *__restrict__ prev_state,
+                                  const int32_t *__restrict__ cu_tok, const int32_t *__restrict__ past, const int32_t *__restrict__ slot,
+                                  const int32_t *__restrict__ seq_of_tok, float *__restrict__ out, int width) {
+  const int t = blockIdx.x, s = seq_of_tok[t], first = cu_tok[s];
+  const int64_t id = ids[t];
+  int64_t r;
+  if (t > first) {
+    r = ((int64_t)ids[t - 1] * mul_prev + id * mul_cur) % buckets;
+  } else {
+    const int sl = slot[s];
+    r = past[s] > 0 ? ((int64_t)prev_state[sl] * mul_prev + id * mul_cur) % buckets : buckets;
+    __syncthreads();                      // every thread has read the slot before it is rewritten
+    if (threadIdx.x == 0) prev_state[sl] = ids[cu_tok[s + 1] - 1];
+  }
+  if (r < 0) r += buckets;
+  const T *row = table + id * width, *extra = pairs + r * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) out[(int64_t)t * width + c] = fmaf(to_f32<T>(row[c]), scale, to_f32<T>(extra[c]));
+}
+
 template <typename T, int VEC>
 __global__ void __launch_bounds__(1024) rms_residual_kernel(const mrs_seq_rms_residual_args a) {
   extern __shared__ __align__(16) float row[];   // [width]
@@ -27,19 +51,41 @@ __global__ void __launch_bounds__(1024) rms_residual_kernel(const mrs_seq_rms_re
   const int n_hist = a.hist ? a.n_hist : 0;
   for (int j = threadIdx.x; j < n_hist; j += blockDim.x) mix[j] = a.mix[j];
   __syncthreads();
+  float inv_y = 1.0f;
+  if (y && a.post_w) {       // the sublayer's output is normed before it is added: its row waits in shared memory as f32
+    float sy = 0.0f;
+    for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+      float yv[VEC];
+      if (VEC == 4) { const float4 q = load4<T>(y + at + c); yv[0] = q.x; yv[1 % VEC] = q.y; yv[2 % VEC] = q.z; yv[3 % VEC] = q.w; }
+      else yv[0] = to_f32<T>(y[at + c]);
+#pragma unroll
+      for (int e = 0; e < VEC; e++) {
+        row[c + e] = yv[e];
+        sy = fmaf(yv[e], yv[e], sy);
+      }
+    }
+    inv_y = rsqrtf_exact(block_sum(sy, red) / (float)width + a.eps);
+  }
   float ss = 0.0f;
   for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
     float v[VEC];
     if (VEC == 4) { const float4 q = *(const float4 *)(a.src + at + c); v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w; }
     else v[0] = a.src[at + c];
-    if (y) {
+    if (y && a.post_w) {     // every thread re-reads the columns it staged itself
+#pragma unroll
+      for (int e = 0; e < VEC; e++) v[e] = fmaf(a.mult, row[c + e] * inv_y * a.post_w[c + e], v[e]);
+    } else if (y) {
       float yv[VEC];
       if (VEC == 4) { const float4 q = load4<T>(y + at + c); yv[0] = q.x; yv[1 % VEC] = q.y; yv[2 % VEC] = q.z; yv[3 % VEC] = q.w; }
       else yv[0] = to_f32<T>(y[at + c]);
 #pragma unroll
       for (int e = 0; e < VEC; e++) v[e] = fmaf(a.mult, yv[e], v[e]);
     }
-    if (a.dst && (y || a.dst != a.src)) {
+    if (a.add_vec) {
+#pragma unroll
+      for (int e = 0; e < VEC; e++) v[e] += a.add_vec[c + e];
+    }
+    if (a.dst && (y || a.add_vec || a.dst != a.src)) {
       if (VEC == 4) *(float4 *)(a.dst + at + c) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
       else a.dst[at + c] = v[0];
     }
@@ -100,6 +146,18 @@ extern "C" int mrs_seq_embed_scaled(const void *table, int dtype, const int32_t 
   return launch_status();
 }
 
+extern "C" int mrs_seq_embed_pair(const void *table, const void *pairs, int dtype, const int32_t *ids, float scale, int64_t buckets,
+                                  int64_t mul_prev, int64_t mul_cur, int32_t *prev_state, const int32_t *cu_tok, const int32_t *past,
+                                  const int32_t *slot, const int32_t *seq_of_tok, float *out, int n_tok, int width, int64_t stream) {
+  if (n_tok <= 0) return 0;
+  if (!table || !pairs || !prev_state || buckets <= 0 || width <= 0) return -2;
+  const int th = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  SEQ_DISPATCH_DTYPE(dtype, (embed_pair_kernel<T><<<n_tok, th, 0, (cudaStream_t)stream>>>((const T *)table, (const T *)pairs, ids, scale, buckets,
+                                                                                        mul_prev, mul_cur, prev_state, cu_tok, past, slot,
+                                                                                        seq_of_tok, out, width)));
+  return launch_status();
+}
+
 extern "C" int mrs_seq_rms_residual(const mrs_seq_rms_residual_args *args, int64_t stream) {
   const mrs_seq_rms_residual_args &a = *args;
   if (a.n_tok <= 0) return 0;
@@ -108,7 +166,7 @@ extern "C" int mrs_seq_rms_residual(const mrs_seq_rms_residual_args *args, int64
   if (bytes > 200 * 1024) return -2;
   auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
   const bool vec = a.width % 4 == 0 && al(a.src) && al(a.dst) && al(a.y) && al(a.hist) && a.hist_stride % 4 == 0 && al(a.mixed) &&
-                   al(a.next_w) && al(a.next_out);
+                   al(a.next_w) && al(a.next_out);      // post_w and add_vec are read one element at a time
   const int items = vec ? a.width / 4 : a.width;
   int th = 64;
   while (th < 1024 && th * (a.n_tok <= 64 ? 1 : 2) < items) th *= 2;    // short batches: one item per thread where possible

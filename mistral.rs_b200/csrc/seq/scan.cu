@@ -6,8 +6,9 @@
 //
 // covers linear attention with a fixed per-head decay (a_t constant, b_t = 1, silu on q / k / v), the state-space
 // form (k = B, q = C, v = x, a_t = exp(-exp(A_log) dt_t), b_t = dt_t, skip = D) and — template flag VD — a forget gate
-// per state ROW that also decides what is written (S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T: the key is the gate's
-// complement and is formed here, in f32, from the same staged row).  The same kernel runs a prompt
+// per state ROW, either with keys of their own (gated linear attention: S_t = diag(f_t) S_(t-1) + k_t v_t^T) or one that
+// also decides what is written (k == NULL: S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, the key is the gate's complement and
+// is formed here, in f32, from the same staged row).  Queries can carry a constant factor (q_scale).  The same kernel runs a prompt
 // portion and a single decoded token: the state is read from the sequence's slot (or taken as zero when the
 // sequence starts), advanced token by token in registers, and written back.
 #include "seq_common.cuh"
@@ -108,7 +109,9 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
   if (VD)
     for (int e = threadIdx.x; e < TC * dks; e += nth) ds[e] = 0.0f;
   const float skip = a.skip ? a.skip[h] : 0.0f;
-  const T *q = (const T *)a.q + g * dk, *k = VD ? nullptr : (const T *)a.k + g * dk, *v = (const T *)a.v + h * dv + col0;
+  const bool own_k = !VD || a.k != nullptr;      // per-row decays with keys of their own, or keys that are the decays' complement
+  const float q_scale = a.q_scale != 0.0f ? a.q_scale : 1.0f;
+  const T *q = (const T *)a.q + g * dk, *k = own_k ? (const T *)a.k + g * dk : nullptr, *v = (const T *)a.v + h * dv + col0;
   const float *dvec = VD ? a.decay_vec + (int64_t)h * dk : nullptr;
   const bool dvec_aligned = VD && dk % 4 == 0 && ((uintptr_t)a.decay_vec & 15) == 0;
   const int vcols = min(cw, dv - col0);
@@ -120,7 +123,7 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
       for (int e = threadIdx.x; e < n * per; e += nth) {
         const int i = e / per, j = e % per;
         cp_async16(rq + i * dkr + j * N, q + (int64_t)(c0 + i) * a.q_ld + j * N);
-        if (!VD) cp_async16(rk + i * dkr + j * N, k + (int64_t)(c0 + i) * a.k_ld + j * N);
+        if (own_k) cp_async16(rk + i * dkr + j * N, k + (int64_t)(c0 + i) * a.k_ld + j * N);
       }
       const int perv = vcols / N;
       for (int e = threadIdx.x; e < n * perv; e += nth) {
@@ -131,7 +134,7 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
       for (int e = threadIdx.x; e < n * dk; e += nth) {
         const int i = e / dk, d = e % dk;
         rq[i * dkr + d] = q[(int64_t)(c0 + i) * a.q_ld + d];
-        if (!VD) rk[i * dkr + d] = k[(int64_t)(c0 + i) * a.k_ld + d];
+        if (own_k) rk[i * dkr + d] = k[(int64_t)(c0 + i) * a.k_ld + d];
       }
       for (int e = threadIdx.x; e < n * vcols; e += nth) {
         const int i = e / vcols, c = e % vcols;
@@ -173,11 +176,11 @@ __global__ void __launch_bounds__(256, RK <= 16 ? (VD ? 2 : 3) : 1) linear_scan_
 #pragma unroll
         for (int x = 0; x < N; x++) {
           const bool in = d0 + x < dk;
-          qs[at + x] = in ? apply_act(to_f32<T>(rq[i * dkr + d0 + x]), a.act) : 0.0f;
+          qs[at + x] = in ? apply_act(to_f32<T>(rq[i * dkr + d0 + x]), a.act) * q_scale : 0.0f;
           if (VD) {
             const float f = in ? rd[i * dkr + d0 + x] : 0.0f;
             ds[at + x] = f;
-            ks[at + x] = in ? 1.0f - f : 0.0f;
+            ks[at + x] = !in ? 0.0f : (own_k ? apply_act(to_f32<T>(rk[i * dkr + d0 + x]), a.act) : 1.0f - f);
           } else {
             ks[at + x] = in ? apply_act(to_f32<T>(rk[i * dkr + d0 + x]), a.act) : 0.0f;
           }
@@ -331,8 +334,8 @@ static int launch_scan(const mrs_seq_scan_args &a, cudaStream_t st) {
                       (size_t)(2 * TC * dkr + TC * cwr) * sizeof(T);
   const size_t tile = (size_t)parts * RK * cw * sizeof(float);
   const size_t bytes = work > tile ? work : tile;
-  const bool aligned = a.dk % N == 0 && a.dv % N == 0 && cw % N == 0 && a.q_ld % N == 0 && (VD || a.k_ld % N == 0) && a.v_ld % N == 0 &&
-                       (uintptr_t)a.q % 16 == 0 && (VD || (uintptr_t)a.k % 16 == 0) && (uintptr_t)a.v % 16 == 0;
+  const bool aligned = a.dk % N == 0 && a.dv % N == 0 && cw % N == 0 && a.q_ld % N == 0 && (!a.k || a.k_ld % N == 0) && a.v_ld % N == 0 &&
+                       (uintptr_t)a.q % 16 == 0 && (uintptr_t)a.k % 16 == 0 && (uintptr_t)a.v % 16 == 0;
   auto kern = linear_scan_kernel<T, RK, TC, VD>;
   static size_t allowed = 48 * 1024;      // per instantiation; raised once per size, so a captured step repeats no attribute call
   if (bytes > allowed) {
@@ -598,7 +601,7 @@ extern "C" int mrs_seq_linear_scan(const mrs_seq_scan_args *args, int64_t stream
   if (a.n_tok <= 0 || a.n_seq <= 0) return 0;
   if (a.heads <= 0 || a.qk_groups <= 0 || a.heads % a.qk_groups || a.dk <= 0 || a.dv <= 0) return -2;
   if (!a.decay_tok && !a.decay_head && !a.decay_vec) return -2;
-  if (a.decay_vec ? (a.decay_tok || a.decay_head || a.qk_groups != a.heads) : !a.k) return -2;
+  if (a.decay_vec ? (a.decay_tok || a.decay_head || a.qk_groups != a.heads) : !a.k) return -2;      // with decay_vec, k is optional
   cudaStream_t st = (cudaStream_t)stream;
   if (a.decay_vec) {
     if (a.dk <= 128) SEQ_DISPATCH_DTYPE(a.dtype, return (launch_scan<T, 16, 16, true>(a, st)));
@@ -708,6 +711,27 @@ extern "C" int mrs_seq_bounded_gate(const void *raw, int64_t raw_ld, int dtype, 
   const int by = (cols + 255) / 256;
   SEQ_DISPATCH_DTYPE(dtype, (bounded_gate_kernel<T><<<dim3(n_tok, by < 64 ? by : 64), 256, 0, (cudaStream_t)stream>>>(
                                 (const T *)raw, raw_ld, bias, lower, cols, gate)));
+  return launch_status();
+}
+
+// gate = sigmoid(raw + bias)^power = exp(power * log_sigmoid(raw + bias)), f32; the logarithm is formed without cancellation
+template <typename T>
+__global__ void power_gate_kernel(const T *__restrict__ raw, int64_t raw_ld, const float *__restrict__ bias, float power, int cols,
+                                  float *__restrict__ gate) {
+  const int t = blockIdx.x;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cols; c += gridDim.y * blockDim.x) {
+    const float z = seq::to_f32<T>(raw[(int64_t)t * raw_ld + c]) + (bias ? bias[c] : 0.0f);
+    const float log_sig = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
+    gate[(int64_t)t * cols + c] = expf(power * log_sig);
+  }
+}
+
+extern "C" int mrs_seq_power_gate(const void *raw, int64_t raw_ld, int dtype, const float *bias, float power, int n_tok, int cols,
+                                  float *gate, int64_t stream) {
+  if (n_tok <= 0 || cols <= 0) return 0;
+  const int by = (cols + 255) / 256;
+  SEQ_DISPATCH_DTYPE(dtype, (power_gate_kernel<T><<<dim3(n_tok, by < 64 ? by : 64), 256, 0, (cudaStream_t)stream>>>(
+                                (const T *)raw, raw_ld, bias, power, cols, gate)));
   return launch_status();
 }
 

@@ -95,6 +95,19 @@ __global__ void rotation_table_kernel(const int32_t *__restrict__ pos_of_tok, co
   cos_sin[e] = make_float2((float)(c * (double)mag), (float)(s * (double)mag));
 }
 
+// Cache row of entry j of a sequence: token position j through the page table, or — pool > 0 — the averaged entry of block j,
+// which sits behind the token rows: per page as many entries as blocks can START in a page, a block at the page of its
+// first position.
+__device__ __forceinline__ int64_t key_row(const int32_t *table, int j, int pool, int page_size, int per_page, int64_t pool_base) {
+  if (pool <= 0) return (int64_t)table[j / page_size] * page_size + j % page_size;
+  const int page = (j * pool) / page_size, first = (page * page_size + pool - 1) / pool;
+  return pool_base + (int64_t)table[page] * per_page + (j - first);
+}
+template <typename T> __device__ __forceinline__ void store_out(T *out, int64_t at, float v, int as_f32) {
+  if (as_f32) ((float *)out)[at] = v;
+  else out[at] = from_f32<T>(v);
+}
+
 // One warp per (token, head).  32 keys per round: lane j scores key j against the whole query (held in shared
 // memory as f32, pre-scaled), the round's maximum and sum go through the warp, then every lane accumulates its
 // value columns over the round's keys.  Softmax statistics and the output accumulate in f32.
@@ -106,7 +119,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
                                                                int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
                                                                const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index,
                                                                int n_tok, T *__restrict__ out, int64_t out_ld, float out_scale, int64_t k_row,
-                                                               int64_t v_row) {
+                                                               int64_t v_row, int pool, int64_t pool_base, int v_shared, int out_f32) {
   extern __shared__ __align__(16) float qsm[];   // [warps][dk]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t job = (int64_t)blockIdx.x * (blockDim.x >> 5) + wib;
@@ -121,15 +134,17 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
   float m = -INFINITY, l = 0.0f, acc[MAX_VCOLS];
 #pragma unroll
   for (int c = 0; c < MAX_VCOLS; c++) acc[c] = 0.0f;
-  const int kept = min(keep_first, lo);                       // kept first keys that lie before the window: [0, kept)
+  // entries before the window: the kept first keys [0, kept), or one averaged entry per whole block of `pool` positions
+  const int kept = pool > 0 ? lo / pool : min(keep_first, lo);
   const int kept_rounds = (kept + 31) / 32, rounds = kept_rounds + (pos - lo) / 32 + 1;
+  const int gv = v_shared ? 0 : g, per_page = pool > 0 ? (page_size + pool - 1) / pool : 0;
   for (int r = 0; r < rounds; r++) {
     const int j0 = r < kept_rounds ? r * 32 : lo + (r - kept_rounds) * 32, jend = r < kept_rounds ? kept : pos + 1;
     const int j = j0 + lane;
     float sc = -INFINITY;
     int64_t slot = 0;
     if (j < jend) {
-      slot = (int64_t)table[j / page_size] * page_size + j % page_size;
+      slot = key_row(table, j, r < kept_rounds ? pool : 0, page_size, per_page, pool_base);
       const T *kr = k_cache + slot * k_row + g * dk;
       float a0 = 0.0f, a1 = 0.0f;
       int d = 0;
@@ -150,7 +165,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
     for (int i = 0; i < n; i++) {
       const float pi = __shfl_sync(0xffffffffu, p, i);
       const int64_t si = __shfl_sync(0xffffffffu, slot, i);
-      const T *vr = v_cache + si * v_row + g * dv;
+      const T *vr = v_cache + si * v_row + gv * dv;
 #pragma unroll
       for (int c = 0; c < MAX_VCOLS; c++)
         if (c * 32 + lane < dv) acc[c] = fmaf(pi, to_f32<T>(vr[c * 32 + lane]), acc[c]);
@@ -161,7 +176,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
   const float inv = out_scale / l;
 #pragma unroll
   for (int c = 0; c < MAX_VCOLS; c++)
-    if (c * 32 + lane < dv) out[(int64_t)t * out_ld + h * dv + c * 32 + lane] = from_f32<T>(acc[c] * inv);
+    if (c * 32 + lane < dv) store_out<T>(out, (int64_t)t * out_ld + h * dv + c * 32 + lane, acc[c] * inv, out_f32);
 }
 
 // The same computation laid out for speed when the head sizes allow vector loads (dk a multiple of 8 and dv even):
@@ -173,7 +188,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache, const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
     float scale, int window, int keep_first, const float *__restrict__ sink, const int32_t *__restrict__ pages, int pages_ld, int page_size,
     const int32_t *__restrict__ seq_of_tok, const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index, T *__restrict__ out,
-    int64_t out_ld, float out_scale, int64_t k_row, int64_t v_row) {
+    int64_t out_ld, float out_scale, int64_t k_row, int64_t v_row, int pool, int64_t pool_base, int v_shared, int out_f32) {
   extern __shared__ __align__(16) float sm[];   // q [dk] | per warp: m, l, acc [VPAIRS * 64]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int ti = blockIdx.x / heads, h = blockIdx.x % heads, t = tok_index ? tok_index[ti] : ti, g = h / (heads / kv_heads);
@@ -188,15 +203,17 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
 #pragma unroll
   for (int c = 0; c < VPAIRS; c++) acc[c] = make_float2(0.0f, 0.0f);
   constexpr int N = Vec16<T>::N;
-  const int kept = min(keep_first, lo);                       // kept first keys that lie before the window: [0, kept)
+  // entries before the window: the kept first keys [0, kept), or one averaged entry per whole block of `pool` positions
+  const int kept = pool > 0 ? lo / pool : min(keep_first, lo);
   const int kept_rounds = (kept + 31) / 32, rounds = kept_rounds + (pos - lo) / 32 + 1;
+  const int gv = v_shared ? 0 : g, per_page = pool > 0 ? (page_size + pool - 1) / pool : 0;
   for (int r = wib; r < rounds; r += SPLIT) {
     const int j0 = r < kept_rounds ? r * 32 : lo + (r - kept_rounds) * 32, jend = r < kept_rounds ? kept : pos + 1;
     const int j = j0 + lane;
     float sc = -INFINITY;
     int64_t slot = 0;
     if (j < jend) {
-      slot = (int64_t)table[j / page_size] * page_size + j % page_size;
+      slot = key_row(table, j, r < kept_rounds ? pool : 0, page_size, per_page, pool_base);
       const T *kr = k_cache + slot * k_row + g * dk;
       float a0 = 0.0f, a1 = 0.0f;
       int d = 0;
@@ -227,7 +244,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
         const float pu = __shfl_sync(0xffffffffu, p, i);
         pi[u] = i0 + u < n ? pu : 0.0f;
         const int64_t si = __shfl_sync(0xffffffffu, slot, i);
-        const T *vr = v_cache + si * v_row + g * dv;               // a lane past n carries slot 0: a valid row, weight 0
+        const T *vr = v_cache + si * v_row + gv * dv;              // a lane past n carries slot 0: a valid row, weight 0
 #pragma unroll
         for (int c = 0; c < VPAIRS; c++)
           vv[u][c] = c * 64 + 2 * lane < dv ? load2<T>(vr + c * 64 + 2 * lane) : make_float2(0.0f, 0.0f);
@@ -262,7 +279,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
       const float mw = part[w * (2 + VPAIRS * 64)];
       if (mw != -INFINITY) o = fmaf(part[w * (2 + VPAIRS * 64) + 2 + c], expf(mw - mx), o);
     }
-    out[(int64_t)t * out_ld + h * dv + c] = from_f32<T>(o * inv);
+    store_out<T>(out, (int64_t)t * out_ld + h * dv + c, o * inv, out_f32);
   }
 }
 
@@ -315,7 +332,8 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
   const int n_tok = a.n_tok, heads = a.heads, kv_heads = a.kv_heads, dk = a.dk, dv = a.dv, dtype = a.dtype;
   if (n_tok <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv > 1024 || dk > 2048 || a.page_size <= 0) return -2;
-  const int keep_first = a.keep_first > 0 ? a.keep_first : 0;
+  const int keep_first = a.keep_first > 0 ? a.keep_first : 0, pool = a.pool > 0 ? a.pool : 0;
+  if (pool > 0 && (a.window <= 0 || keep_first > 0)) return -2;      // averaged blocks lie before a window and replace kept first keys
   cudaStream_t st = (cudaStream_t)stream;
   const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
   const int64_t k_row = a.k_row > 0 ? a.k_row : (int64_t)kv_heads * dk, v_row = a.v_row > 0 ? a.v_row : (int64_t)kv_heads * dv;
@@ -326,7 +344,8 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
 #define SEQ_ATTN_VEC(VP)                                                                                                         \
   window_attention_vec_kernel<T, VP, SPLIT><<<(unsigned)n_tok * heads, SPLIT * 32, (dk + SPLIT * (2 + VP * 64)) * sizeof(float), st>>>( \
       (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink,  \
-      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row)
+      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row, pool,     \
+      a.pool_base, a.v_shared, a.out_f32)
     SEQ_DISPATCH_DTYPE(dtype, {
       if (dv <= 64) SEQ_ATTN_VEC(1);
       else if (dv <= 128) SEQ_ATTN_VEC(2);
@@ -341,7 +360,8 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
 #define SEQ_ATTN_LAUNCH(VC)                                                                                              \
   window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float), st>>>(  \
       (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink, \
-      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, n_tok, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row)
+      a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, n_tok, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row, pool, \
+      a.pool_base, a.v_shared, a.out_f32)
   SEQ_DISPATCH_DTYPE(dtype, {
     if (dv <= 64) SEQ_ATTN_LAUNCH(2);
     else if (dv <= 128) SEQ_ATTN_LAUNCH(4);

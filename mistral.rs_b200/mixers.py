@@ -5,7 +5,10 @@ norm per head or over the whole projection, rotary positions with scaled frequen
 sink, values that are the keys), attention through a shared low-rank latent (one cached latent per token, which a later
 layer may reuse), a linear recurrence whose per-channel forget gate also writes (HGRN2), a short causal convolution added
 to a sublayer's input, a Mamba-2 style state-space mixer, two mixers side by side, dense GLU / plain and routed-expert
-feed-forwards (softmax or sigmoid routing, groups scored by their best or their few best experts, plain or capped GLU).
+feed-forwards (softmax or sigmoid routing, groups scored by their best or their few best experts, plain or capped GLU),
+a token shift (a sublayer's input blended with its predecessor's), gated linear attention with a decay per key channel,
+attention whose far past is seen as averaged blocks and whose softmax weights are mixed across heads, output gates per
+entry or per head.
 
 A mechanism owns its device weights and declares the per-layer cache it needs (`alloc_cache`): token-indexed pages
 (sized by the engine's block pool) and / or per-request state slots (sized by the engine's slot pool).  `forward`
@@ -63,7 +66,7 @@ class Rotation:
     make pair i, (i, i + dims / 2) or the neighbours (2i, 2i + 1), is the choice of the kernel that applies the table.
     `scaling` (YaRN: factor, original, fast, slow) divides the slow frequencies by `factor` along a linear ramp between
     the pair indices at which `original` positions make `fast` and `slow` turns, and multiplies cos and sin by
-    0.1 ln(factor) + 1.  Frequencies are formed in double on the host; the table of a step (one per distinct
+    0.1 ln(factor) + 1; with the keys factor, original, low, high it is the wavelength rule instead (no magnitude).  Frequencies are formed in double on the host; the table of a step (one per distinct
     rotation, shared by the layers that use it) comes from `seq_ops.rotation_table`."""
 
     def __init__(self, dims, base, scaling, device):
@@ -72,7 +75,22 @@ class Rotation:
         if dims < 2 or dims % 2:
             raise ValueError("rotated dimensions come in pairs")
         freq, self.mag = [base ** (-2.0 * i / dims) for i in range(dims // 2)], 1.0
-        if scaling:
+        if scaling and "low" in scaling:
+            # by wavelength (the rule of Llama 3.1): shorter than original / high: kept; longer than original / low: divided by
+            # factor; between, a linear blend in original / wavelength
+            factor, orig, low, high = (float(scaling[k]) for k in ("factor", "original", "low", "high"))
+            scaled = []
+            for f in freq:
+                wave = 2.0 * math.pi / f
+                if wave < orig / high:
+                    scaled.append(f)
+                elif wave > orig / low:
+                    scaled.append(f / factor)
+                else:
+                    t = (orig / wave - low) / (high - low)
+                    scaled.append((1.0 - t) * f / factor + t * f)
+            freq = scaled
+        elif scaling:
             factor, orig = float(scaling["factor"]), float(scaling["original"])
             turn = lambda t: dims * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(base))
             lo, hi = max(math.floor(turn(float(scaling["fast"]))), 0), min(math.ceil(turn(float(scaling["slow"]))), dims - 1)
@@ -95,10 +113,22 @@ class WindowAttention:
     heads (`norm_mode` QK_NORM_HEAD), over the whole projection at once (QK_NORM_WHOLE) or none; then `rotation` (None:
     scores carry no position).  Scores are scaled by a given constant.  Position i sees j <= i with i - j < `window`
     (0: full causal) or j < `keep_first`; `sink` [heads] adds exp(sink) to the softmax denominator.  With
-    `values_from_keys` there is no value projection: the values are the keys as projected, before norm and rotation."""
+    `values_from_keys` there is no value projection: the values are the keys as projected, before norm and rotation.
+
+    `pool` > 0 (needs a window and the page size): the positions before the window are seen block-wise — one key and one
+    value per block of `pool` positions that lies wholly before the window, each the mean of the block's cached keys /
+    values; tokens that left the window while their block is incomplete from the query's point of view are not seen.  The
+    means live behind the token rows of the same cache tensors and are formed when a block's last position is stored.
+
+    `talk` [heads, heads] f32: the softmax weights are mixed across heads afterwards, w'_h = sum_g talk[h, g] w_g, and head h
+    applies w'_h to the values of its own key/value head (a sink's share is not mixed).  Computed through linearity: the
+    attention kernel applies every head's weights to all value heads in f32, `seq_ops.mix_heads` sums over g."""
 
     def __init__(self, heads, kv_heads, dk, dv, scale, window, q_norm_w, k_norm_w, eps, norm_mode=K.QK_NORM_HEAD, rotation=None,
-                 keep_first=0, sink=None, values_from_keys=False):
+                 keep_first=0, sink=None, values_from_keys=False, pool=0, talk=None, page_size=None):
+        if pool > 0 and (window <= 0 or keep_first > 0 or not page_size):
+            raise ValueError("averaged blocks need a window, no kept first tokens, and the page size")
+        self.pool, self.talk, self.pool_page_size, self.pool_base = int(pool), talk, page_size, 0
         if values_from_keys and dk != dv:
             raise ValueError("values that are the keys need equal key and value head sizes")
         if heads % kv_heads:
@@ -113,22 +143,53 @@ class WindowAttention:
         return self.heads * self.dk + self.kv_heads * self.dk + (0 if self.values_from_keys else self.kv_heads * self.dv)
 
     def alloc_cache(self, n_slots, n_token_slots, dtype, device):
-        return {"k": torch.zeros(n_token_slots, self.kv_heads, self.dk, dtype=dtype, device=device),
-                "v": torch.zeros(n_token_slots, self.kv_heads, self.dv, dtype=dtype, device=device)}
+        rows = n_token_slots
+        if self.pool > 0:                      # the averaged blocks' rows follow the token rows
+            self.pool_base = n_token_slots
+            rows += K.pool_rows(n_token_slots, self.pool_page_size, self.pool)
+        return {"k": torch.zeros(rows, self.kv_heads, self.dk, dtype=dtype, device=device),
+                "v": torch.zeros(rows, self.kv_heads, self.dv, dtype=dtype, device=device)}
 
-    def attend(self, y, col0, batch, cache, page_size, out, out_col=0, out_scale=1.0):
+    def attend(self, y, col0, batch, cache, page_size, out, out_col=0, out_scale=1.0, gate_col=None, gate_act=K.ACT_SIGMOID):
         """y holds q | k | v (q | k when the values are the keys) from column col0; writes heads * dv columns of `out`
         from out_col.  Keys and values of the new tokens are normed, rotated and stored first.  Long portions (32 tokens
         or more) run on tensor cores when they fit (bf16, equal head sizes of 64 or 128, 16-byte aligned rows): when every
         one of them starts its sequence and the layer has neither sink nor kept first tokens, on the package's prompt
         kernels over the fresh q / k / v; otherwise — sinks, kept tokens, portions that continue a sequence — on the
         sequence library's prompt kernel, which reads keys and values from the pages.  Every other token (short portions,
-        decoded tokens, other head sizes, f32) runs on the (token, head) kernel over the pages."""
+        decoded tokens, other head sizes, f32) runs on the (token, head) kernel over the pages, and so does every token of a
+        layer with averaged blocks or mixed heads.  gate_col: columns of y (heads * dv of them) whose `gate_act` multiplies the
+        result entry by entry."""
         kc = col0 + self.heads * self.dk
         vc = None if self.values_from_keys else kc + self.kv_heads * self.dk
         cos_sin = self.rotation.table(batch) if self.rotation is not None else None
         K.attention_prepare(y, col0, kc, vc, self.norm_mode, self.q_norm_w, self.k_norm_w, self.eps, self.heads, self.kv_heads, self.dk,
                             self.dv, cache["k"], cache["v"], batch.slot_of_tok, cos_sin, self.rotation.dims if cos_sin is not None else 0)
+        if self.pool > 0:
+            if page_size != self.pool_page_size or cache["k"].shape[0] <= self.pool_base:
+                raise ValueError("the cache was not made for this layer's averaged blocks")
+            K.pool_blocks(cache["k"], cache["v"], self.kv_heads * self.dk, self.kv_heads * self.dv, self.pool, self.pool_base, batch, page_size)
+        if self.pool > 0 or self.talk is not None:
+            self._attend_general(y, col0, batch, cache, page_size, out, out_col, out_scale, gate_col, gate_act)
+            return
+        self._attend_plain(y, col0, kc, vc, batch, cache, page_size, out, out_col, out_scale)
+        if gate_col is not None:
+            K.gate_cols(out[:, out_col:], y, gate_col, self.heads * self.dv, 1, gate_act)
+
+    def _attend_general(self, y, col0, batch, cache, page_size, out, out_col, out_scale, gate_col, gate_act):
+        H, G, dv = self.heads, self.kv_heads, self.dv
+        if self.talk is None:
+            K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, dv, self.scale, self.window, self.keep_first, self.sink, batch,
+                              page_size, out, out_col, out_scale, pool=self.pool, pool_base=self.pool_base)
+            if gate_col is not None:
+                K.gate_cols(out[:, out_col:], y, gate_col, H * dv, 1, gate_act)
+            return
+        every = torch.empty(y.shape[0], H * G * dv, dtype=torch.float32, device=y.device)      # head g's weights on every value head
+        K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, G * dv, self.scale, self.window, self.keep_first, self.sink, batch,
+                          page_size, every, 0, out_scale, v_row=G * dv, pool=self.pool, pool_base=self.pool_base, v_shared=True)
+        K.mix_heads(every, self.talk, H, G, dv, out[:, out_col:], y if gate_col is not None else None, gate_col or 0, gate_act)
+
+    def _attend_plain(self, y, col0, kc, vc, batch, cache, page_size, out, out_col, out_scale):
         tok_index = None
         aligned = all(v % 8 == 0 for v in (y.stride(0), col0, out.stride(0), out_col))
         if batch.long and y.dtype == torch.bfloat16 and self.dk == self.dv and self.dk in (64, 128) and aligned:
@@ -166,6 +227,16 @@ class InputConvolution:
         return K.causal_conv(h, 0, self.taps.shape[0], self.taps, None, K.ACT_NONE, state, batch)
 
 
+class TokenShift(InputConvolution):
+    """h <- h + (h_prev - h) * mu: every channel of a sublayer's input is blended with the same channel of the previous
+    token's (unshifted) input, zeros before a sequence's first token.  It is the two-tap case of the input convolution,
+    h + (mu * h_prev - mu * h); the previous input of every request is state (one slot each)."""
+
+    def __init__(self, mu):
+        mu = mu.to(torch.float32).reshape(-1, 1)
+        super().__init__(torch.cat([mu, -mu], dim=1))
+
+
 class LatentAttentionMixer:
     """Multi-head latent attention.  Queries: c_q = rms_norm(W_dq h) w, q = W_uq c_q, per head [dn plain | dr rotated].
     Keys / values: W_dkv h = [kv_rank | dr]; c = rms_norm(first part) w is the latent, the last dr entries (rotated, not
@@ -177,10 +248,15 @@ class LatentAttentionMixer:
     over the cached rows as one key/value head whose values are the rows' first kv_rank columns, and W_uv,h maps the
     result to the head's output.  In bf16 every sequence of a step, a prompt portion or a single decoded token, runs on the
     tensor-core latent kernel (all heads of a token share one fetched key tile); f32, and sizes the kernel does not take,
-    run on the (token, head) kernel over the pages.  `shares`: this mixer has no W_dkv and reads the cache another layer fills."""
+    run on the (token, head) kernel over the pages.  `shares`: this mixer has no W_dkv and reads the cache another layer fills.
+
+    q_rank 0: there is no query latent — w_down's first heads * (dn + dr) rows are the query projection itself (w_uq and
+    q_norm_w are None).  dr 0 with rotation None: no rotated part, scores carry no position.  `head_gate`: w_down ends with
+    `heads` more rows, and head h's output is multiplied by that activation of row h's product (a gate per head)."""
 
     def __init__(self, w_down, w_uq, w_uk, w_uv, w_o, q_norm_w, kv_norm_w, heads, dn, dr, dv, q_rank, kv_rank, scale, window, rotation, eps,
-                 page_size, shares=False):
+                 page_size, shares=False, head_gate=None):
+        self.head_gate = head_gate
         self.w_down, self.w_uq, self.w_o, self.q_norm_w, self.kv_norm_w = w_down, w_uq, w_o, q_norm_w, kv_norm_w
         self.w_uk = w_uk.view(heads, dn, kv_rank)                       # [H][dn][r]: q_plain,h @ w_uk[h] = W_uk,h^T q_plain,h
         self.w_uv_t = w_uv.view(heads, dv, kv_rank).transpose(1, 2)     # [H][r][dv]
@@ -199,14 +275,22 @@ class LatentAttentionMixer:
         latent = cache["latent"]
         cos_sin = self.rotation.table(batch) if self.rotation is not None else None
         rot_dims = self.rotation.dims if self.rotation is not None else 0
-        y = linear(h, self.w_down)                                           # query latent | (key/value latent | shared key part)
-        cq = torch.empty(T, self.q_rank, dtype=h.dtype, device=h.device)
-        K.latent_prepare(y, 0, self.q_rank, self.q_norm_w, cq, self.q_rank, 0 if self.shares else R, dr, rot_dims, self.kv_norm_w, cos_sin,
-                         self.eps, latent, batch.slot_of_tok)
-        q = linear(cq, self.w_uq).view(T, H, dn + dr)
+        y = linear(h, self.w_down)                                           # query latent (or queries) | (key/value latent | shared key part) | (gates)
+        q_cols = self.q_rank if self.q_rank > 0 else H * (dn + dr)
+        if self.q_rank > 0:
+            cq = torch.empty(T, self.q_rank, dtype=h.dtype, device=h.device)
+            K.latent_prepare(y, 0, self.q_rank, self.q_norm_w, cq, q_cols, 0 if self.shares else R, dr, rot_dims, self.kv_norm_w, cos_sin,
+                             self.eps, latent, batch.slot_of_tok)
+            q2 = linear(cq, self.w_uq)
+        else:
+            if not self.shares:
+                K.latent_prepare(y, 0, 0, None, None, q_cols, R, dr, rot_dims, self.kv_norm_w, cos_sin, self.eps, latent, batch.slot_of_tok)
+            q2 = y[:, :q_cols]
+        q = q2.unflatten(1, (H, dn + dr))
         qa = torch.empty(T, H, self.row, dtype=h.dtype, device=h.device)      # the absorbed queries
         torch.bmm(q[:, :, :dn].transpose(0, 1), self.w_uk, out=qa[:, :, :R].transpose(0, 1))
-        K.rotate_pairs(q.view(T, -1), dn, dn + dr, qa.view(T, -1), R, self.row, H, dr, rot_dims, cos_sin)
+        if dr > 0:
+            K.rotate_pairs(q2, dn, dn + dr, qa.view(T, -1), R, self.row, H, dr, rot_dims, cos_sin)
         o = torch.empty(T, H, R, dtype=h.dtype, device=h.device)
         if h.dtype == torch.bfloat16 and K.latent_attention_fits(R, dr) and latent.stride(0) % 8 == 0:
             K.latent_prompt_attention(qa.view(T, -1), latent, H, R, dr, self.scale, self.window, batch, self.page_size, o.view(T, -1))
@@ -214,6 +298,9 @@ class LatentAttentionMixer:
             K.latent_attention(qa.view(T, -1), latent, H, R, dr, self.scale, self.window, batch, self.page_size, o.view(T, -1))
         out = torch.empty(T, H, self.dv, dtype=h.dtype, device=h.device)
         torch.bmm(o.transpose(0, 1), self.w_uv_t, out=out.transpose(0, 1))
+        if self.head_gate is not None:
+            gate_col = q_cols + (0 if self.shares else R + dr)
+            K.gate_cols(out.view(T, H * self.dv), y, gate_col, H * self.dv, self.dv, self.head_gate)
         return linear(out.view(T, H * self.dv), self.w_o)
 
 
@@ -242,12 +329,41 @@ class TiedGateMixer:
         return linear(on, self.w_o)
 
 
+class GatedLinearAttentionMixer:
+    """Linear attention with a decay per key channel: q = W_q h * q_scale, k = W_k h, v = W_v h; per head and key channel
+    alpha = sigmoid(W_a2 (W_a1 h) + b)^(1 / tau), formed in f32 from the low-rank projection's output; S_t = diag(alpha_t)
+    S_(t-1) + k_t v_t^T, o_t = S_t^T q_t; every head's o is RMS-normed over its value size with weights shared by the heads,
+    multiplied by silu(W_g h), and projected.  The recurrence is the package's linear scan with a decay per state row and keys
+    of their own.  w_in rows: q | k | v | g | a1."""
+
+    def __init__(self, w_in, w_a2, a_bias, tau, w_o, norm_w, heads, dk, dv, q_scale, eps, low_rank):
+        self.w_in, self.w_a2, self.a_bias, self.inv_tau, self.w_o = w_in, w_a2, a_bias, 1.0 / float(tau), w_o
+        self.norm_w = norm_w.repeat(heads).contiguous()            # the group norm takes one weight per column
+        self.heads, self.dk, self.dv, self.q_scale, self.eps, self.low_rank = heads, dk, dv, float(q_scale), eps, low_rank
+
+    def alloc_cache(self, n_slots, n_token_slots, dtype, device):
+        return {"state": torch.zeros(n_slots, self.heads, self.dk, self.dv, dtype=torch.float32, device=device)}
+
+    def forward(self, h, batch, cache):
+        H, dk, dv = self.heads, self.dk, self.dv
+        y = linear(h, self.w_in)                                           # [T, 2 H dk + 2 H dv + r]: q | k | v | g | a1
+        g_col = 2 * H * dk + H * dv
+        z = linear(y[:, g_col + H * dv:g_col + H * dv + self.low_rank], self.w_a2)
+        alpha = K.power_gate(z, 0, H * dk, self.a_bias, self.inv_tau)
+        o = K.linear_scan(y, 0, y, H * dk, y, 2 * H * dk, H, H, dk, dv, cache["state"], batch, decay_vec=alpha, q_scale=self.q_scale)
+        on = torch.empty(h.shape[0], H * dv, dtype=h.dtype, device=h.device)
+        K.gated_group_norm(o, y, g_col, self.norm_w, H, self.eps, K.ACT_SILU, False, on)
+        return linear(on, self.w_o)
+
+
 class AttentionMixer:
     """A `WindowAttention` with its own projections: one input GEMM for q | k | v (optionally biased), attention,
-    output projection (optionally biased)."""
+    output projection (optionally biased).  `gate_act`: w_in has heads * dv more rows after q | k | v, and the attention's
+    result is multiplied entry by entry with that activation of them before the output projection."""
 
-    def __init__(self, attn: WindowAttention, w_in, w_out, page_size, b_in=None, b_out=None):
+    def __init__(self, attn: WindowAttention, w_in, w_out, page_size, b_in=None, b_out=None, gate_act=None):
         self.attn, self.w_in, self.w_out, self.b_in, self.b_out, self.page_size = attn, w_in, w_out, b_in, b_out, page_size
+        self.gate_act = gate_act
 
     def alloc_cache(self, n_slots, n_token_slots, dtype, device):
         return self.attn.alloc_cache(n_slots, n_token_slots, dtype, device)
@@ -255,7 +371,10 @@ class AttentionMixer:
     def forward(self, h, batch, cache):
         y = F.linear(h, self.w_in, self.b_in)
         o = torch.empty(h.shape[0], self.attn.heads * self.attn.dv, dtype=h.dtype, device=h.device)
-        self.attn.attend(y, 0, batch, cache, self.page_size, o)
+        if self.gate_act is None:
+            self.attn.attend(y, 0, batch, cache, self.page_size, o)
+        else:
+            self.attn.attend(y, 0, batch, cache, self.page_size, o, gate_col=self.attn.proj_cols, gate_act=self.gate_act)
         return F.linear(o, self.w_out, self.b_out)
 
 

@@ -49,6 +49,11 @@ def _load_fosulix(model_dir, device, dtype, **options):
     return FosulixModel.from_dir(model_dir, device, dtype, **options)
 
 
+def _load_kibotar(model_dir, device, dtype, **options):
+    from .kibotar import KibotarModel
+    return KibotarModel.from_dir(model_dir, device, dtype, **options)
+
+
 def _load_llama(model_dir, device, dtype, **options):
     """Llama-family UQFF folder (config.json + *.uqff shards + residual.safetensors) -> `model.LlamaWeights`, the object
     `model.LlamaRunner` / `model.LlamaPrefill` drive."""
@@ -66,5 +71,6 @@ def _load_llama(model_dir, device, dtype, **options):
 register("Nisasun", _load_nisasun)
 register("Kilizen", _load_kilizen)
 register("Fosulix", _load_fosulix)
+register("Kibotar", _load_kibotar)
 for _name in ("LlamaForCausalLM", "MistralForCausalLM", "llama", "mistral"):
     register(_name, _load_llama)

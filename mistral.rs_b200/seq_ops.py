@@ -54,7 +54,7 @@ class ScanArgs(ctypes.Structure):
                 ("cu_tok", ctypes.c_void_p), ("past", ctypes.c_void_p), ("slot", ctypes.c_void_p),
                 ("n_seq", ctypes.c_int), ("n_tok", ctypes.c_int), ("out", ctypes.c_void_p),
                 ("seg_state", ctypes.c_void_p), ("seg_decay", ctypes.c_void_p), ("seg_len", ctypes.c_int), ("n_segs", ctypes.c_int),
-                ("decay_vec", ctypes.c_void_p)]
+                ("decay_vec", ctypes.c_void_p), ("q_scale", ctypes.c_float)]
 
 
 class GluRule(ctypes.Structure):
@@ -75,7 +75,7 @@ class RmsResidualArgs(ctypes.Structure):
     _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("y", ctypes.c_void_p), ("mult", ctypes.c_float),
                 ("hist", ctypes.c_void_p), ("hist_stride", ctypes.c_int64), ("n_hist", ctypes.c_int), ("mix", ctypes.c_void_p),
                 ("mixed", ctypes.c_void_p), ("next_w", ctypes.c_void_p), ("eps", ctypes.c_float), ("next_out", ctypes.c_void_p),
-                ("dtype", ctypes.c_int), ("n_tok", ctypes.c_int), ("width", ctypes.c_int)]
+                ("dtype", ctypes.c_int), ("n_tok", ctypes.c_int), ("width", ctypes.c_int), ("post_w", ctypes.c_void_p), ("add_vec", ctypes.c_void_p)]
 
 
 class LatentPrepareArgs(ctypes.Structure):
@@ -102,7 +102,8 @@ class PagedAttentionArgs(ctypes.Structure):
                 ("pages", ctypes.c_void_p), ("pages_ld", ctypes.c_int), ("page_size", ctypes.c_int),
                 ("seq_of_tok", ctypes.c_void_p), ("pos_of_tok", ctypes.c_void_p), ("tok_index", ctypes.c_void_p), ("n_tok", ctypes.c_int),
                 ("out", ctypes.c_void_p), ("out_ld", ctypes.c_int64), ("out_scale", ctypes.c_float),
-                ("k_row", ctypes.c_int64), ("v_row", ctypes.c_int64)]
+                ("k_row", ctypes.c_int64), ("v_row", ctypes.c_int64), ("pool", ctypes.c_int), ("pool_base", ctypes.c_int64),
+                ("v_shared", ctypes.c_int), ("out_f32", ctypes.c_int)]
 
 
 SCAN_SEGMENT = 256                  # tokens per segment when a long portion is scanned as segments side by side
@@ -187,6 +188,15 @@ def bounded_gate(y, col0, cols, bias, lower):
     return out
 
 
+def power_gate(y, col0, cols, bias, power):
+    """f32 [T, cols]: sigmoid(y[:, col0:col0 + cols] + bias) ** power, formed as exp(power * log_sigmoid(.))."""
+    T = y.shape[0]
+    out = torch.empty(T, cols, dtype=torch.float32, device=y.device)
+    _ok(lib().mrs_seq_power_gate(_p(y, col0), _l(y.stride(0)), _i(DTYPE_CODE[y.dtype]), _p(bias), _f(power), _i(T), _i(cols), _p(out), _st(y)),
+        "power_gate")
+    return out
+
+
 def gated_group_norm(x, gate, gate_col, weight, groups, eps, gate_act, gate_first, out, out_col=0, out_scale=1.0):
     """x f32 [T, C]; the gate is columns gate_col.. of `gate`; writes columns out_col.. of `out`."""
     T, C = x.shape
@@ -219,9 +229,10 @@ def ssm_steps(inp, col0, bias, a_log):
 
 
 def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, batch, act=ACT_NONE, decay_tok=None, decay_head=None,
-                scale_tok=None, skip=None, decay_vec=None):
+                scale_tok=None, skip=None, decay_vec=None, q_scale=1.0):
     """q / k / v are column ranges (starting at *_col) of 2-D activation tensors; returns o f32 [T, heads * dv].
-    decay_vec f32 [T, heads * dk] (then k is None): every state row has its own decay and the key is its complement."""
+    decay_vec f32 [T, heads * dk]: every state row has its own decay; with k None the key is the decay's complement.
+    q_scale: a constant factor on the queries (applied in f32)."""
     T = q.shape[0]
     out = torch.empty(T, heads * dv, dtype=torch.float32, device=q.device)
     a = ScanArgs()
@@ -229,7 +240,7 @@ def linear_scan(q, q_col, k, k_col, v, v_col, heads, qk_groups, dk, dv, state, b
     a.q_ld, a.v_ld = q.stride(0), v.stride(0)
     if k is not None:
         a.k, a.k_ld = _p(k, k_col).value, k.stride(0)
-    a.decay_vec = _p(decay_vec).value
+    a.decay_vec, a.q_scale = _p(decay_vec).value, float(q_scale)
     a.dtype, a.act = DTYPE_CODE[q.dtype], act
     a.heads, a.qk_groups, a.dk, a.dv = heads, qk_groups, dk, dv
     a.decay_tok, a.decay_head = _p(decay_tok).value, _p(decay_head).value
@@ -395,12 +406,17 @@ def attention_prepare(y, q_col, k_col, v_col, norm_mode, q_norm_w, k_norm_w, eps
 
 
 def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, keep_first, sink, batch, page_size, out, out_col=0,
-                    out_scale=1.0, tok_index=None, k_row=0, v_row=0):
+                    out_scale=1.0, tok_index=None, k_row=0, v_row=0, pool=0, pool_base=0, v_shared=False):
     """Every token of the step (or those listed in tok_index) against the pages of its sequence: position i sees j <= i
     with i - j < window (0: all) or j < keep_first; sink [heads] f32 or None.  k_row / v_row: elements between the cache
-    rows of neighbouring slots (0: kv_heads * dk / kv_heads * dv)."""
+    rows of neighbouring slots (0: kv_heads * dk / kv_heads * dv).  pool > 0: besides the window, one averaged entry per
+    block of `pool` positions wholly before it, read from cache rows pool_base.. (`pool_blocks`).  v_shared: every head
+    reads value columns [0, dv) of a row — dv is then all value heads side by side.  An f32 `out` is written as f32 whatever
+    the activation type."""
     a = PagedAttentionArgs()
     a.k_row, a.v_row = int(k_row), int(v_row)
+    a.pool, a.pool_base, a.v_shared = int(pool), int(pool_base), int(bool(v_shared))
+    a.out_f32 = int(out.dtype == torch.float32 and y.dtype != torch.float32)
     a.q, a.q_ld, a.k_cache, a.v_cache = _p(y, q_col).value, y.stride(0), k_cache.data_ptr(), v_cache.data_ptr()
     a.dtype, a.heads, a.kv_heads, a.dk, a.dv = DTYPE_CODE[y.dtype], heads, kv_heads, dk, dv
     a.scale, a.window, a.keep_first, a.sink = scale, int(window), int(keep_first), _p(sink).value
@@ -409,6 +425,31 @@ def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, 
     a.n_tok = y.shape[0] if tok_index is None else tok_index.numel()
     a.out, a.out_ld, a.out_scale = _p(out, out_col).value, out.stride(0), out_scale
     _ok(lib().mrs_seq_paged_attention(ctypes.byref(a), _st(y)), "paged_attention")
+
+
+def pool_rows(n_token_slots, page_size, pool):
+    """Cache rows that the averaged blocks of a pool of n_token_slots token rows need (per page: as many as blocks can start in one)."""
+    return (n_token_slots // page_size) * (-(-page_size // pool))
+
+
+def pool_blocks(k_cache, v_cache, k_cols, v_cols, pool, pool_base, batch, page_size):
+    """For every token of the step that ends a block of `pool` positions: the block's mean key / value row -> its cache row."""
+    _ok(lib().mrs_seq_pool_blocks(_p(k_cache), _p(v_cache), _i(DTYPE_CODE[k_cache.dtype]), _l(k_cols), _l(v_cols), _i(k_cols), _i(v_cols),
+                                  _i(pool), _l(pool_base), _p(batch.pages), _i(batch.pages.shape[1]), _i(page_size), _p(batch.seq_of_tok),
+                                  _p(batch.pos_of_tok), _i(batch.n_tok), _st(k_cache)), "pool_blocks")
+
+
+def mix_heads(a, mix, heads, kv_heads, dv, out, gate=None, gate_col=0, gate_act=ACT_NONE):
+    """out[t, h] = act(gate[t, h]) * sum_g mix[h, g] * a[t, g, value head of h]; a f32 [T, heads * kv_heads * dv]."""
+    _ok(lib().mrs_seq_mix_heads(_p(a), _p(mix), _p(gate, gate_col) if gate is not None else _p(None), _l(gate.stride(0) if gate is not None else 0),
+                                _i(gate_act), _p(out), _l(out.stride(0)), _i(DTYPE_CODE[out.dtype]), _i(heads), _i(kv_heads), _i(dv),
+                                _i(out.shape[0]), _st(out)), "mix_heads")
+
+
+def gate_cols(x, gate, gate_col, cols, group, act):
+    """x[:, c] *= act(gate[:, gate_col + c // group]) in place for c < cols."""
+    _ok(lib().mrs_seq_gate_cols(_p(x), _l(x.stride(0)), _p(gate, gate_col), _l(gate.stride(0)), _i(DTYPE_CODE[x.dtype]), _i(cols), _i(group),
+                                _i(act), _i(x.shape[0]), _st(x)), "gate_cols")
 
 
 def prompt_attention(y, q_col, k_cache, v_cache, batch, page_size, heads, kv_heads, d, scale, window, keep_first, sink, out, out_col=0):
@@ -477,9 +518,21 @@ def embed_scaled(table, ids, scale, out):
     return out
 
 
-def rms_residual(src, y=None, mult=1.0, dst=None, hist=None, n_hist=0, mix=None, mixed=None, next_w=None, eps=0.0, dtype=None):
-    """One pass over an f32 residual [T, W]: v = src + mult * y -> dst; v = sum_j mix[j] * hist[j] (hist f32 [>= n_hist, T, W],
-    dst may be one of its entries) -> mixed; returns rms_norm(v) * next_w in the activation type when next_w is given."""
+def embed_pair(table, pairs, ids, scale, buckets, mul_prev, mul_cur, prev_state, batch, out):
+    """out f32 [T, W] = table[ids] * scale + pairs[hash of (previous token, token)]; the table's last row for a sequence's first
+    token; prev_state int32 [slots] carries every request's last token from step to step."""
+    T, W = ids.numel(), table.shape[1]
+    _ok(lib().mrs_seq_embed_pair(_p(table), _p(pairs), _i(DTYPE_CODE[table.dtype]), _p(ids), _f(scale), _l(buckets), _l(mul_prev), _l(mul_cur),
+                                 _p(prev_state), _p(batch.cu_tok), _p(batch.past), _p(batch.slot), _p(batch.seq_of_tok), _p(out), _i(T), _i(W),
+                                 _st(table)), "embed_pair")
+    return out
+
+
+def rms_residual(src, y=None, mult=1.0, dst=None, hist=None, n_hist=0, mix=None, mixed=None, next_w=None, eps=0.0, dtype=None, post_w=None,
+                 add_vec=None):
+    """One pass over an f32 residual [T, W]: v = src + mult * y (y first RMS-normed with post_w when given) + add_vec [W] -> dst;
+    v = sum_j mix[j] * hist[j] (hist f32 [>= n_hist, T, W], dst may be one of its entries) -> mixed; returns rms_norm(v) * next_w
+    in the activation type when next_w is given."""
     T, W = src.shape
     dtype = y.dtype if y is not None else dtype
     out = torch.empty(T, W, dtype=dtype, device=src.device) if next_w is not None else None
@@ -489,6 +542,7 @@ def rms_residual(src, y=None, mult=1.0, dst=None, hist=None, n_hist=0, mix=None,
         a.hist, a.hist_stride, a.n_hist, a.mix = _p(hist).value, hist.stride(0), int(n_hist), _p(mix).value
     a.mixed, a.next_w, a.eps, a.next_out = _p(mixed).value, _p(next_w).value, float(eps), _p(out).value
     a.dtype, a.n_tok, a.width = DTYPE_CODE[dtype], T, W
+    a.post_w, a.add_vec = _p(post_w).value, _p(add_vec).value
     _ok(lib().mrs_seq_rms_residual(ctypes.byref(a), _st(src)), "rms_residual")
     return out
 
