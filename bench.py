@@ -956,6 +956,228 @@ def bench_fosulix(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
     return out
 
 
+# ------------------------------------------------------------------------------------------- --arch kibotar
+def kibotar_bench_config(width, vocab=32000):
+    """Four layers at sizes of a real model's layers of this width: latent attention (causal, a gate per head), attention over a
+    window plus averaged blocks with head-mixed weights, gated linear attention, latent attention; dense feed-forwards of four
+    times the width; the last three layers form a repeated range of one pass (its step vector is added before it)."""
+    H = width // 128
+    lat = {"heads": H, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5}
+    att = {"heads": H, "kv_heads": max(1, H // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024, "pool": 8},
+           "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    gla = {"heads": H, "dim": 128, "vdim": 128, "tau": 16.0}
+    mlp = {"kind": "dense", "ff": 4 * width}
+    return {"architecture": "Kibotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 127}},
+            "loop": {"start": 1, "stop": 4, "times": 1},
+            "layers": [{"type": "latent_attention", "mixer": lat, "mlp": mlp}, {"type": "attention", "mixer": att, "mlp": mlp},
+                       {"type": "gla", "mixer": gla, "mlp": mlp}, {"type": "latent_attention", "mixer": lat, "mlp": mlp}]}
+
+
+def engine_bench_tools(torch, dev, steps, warmup, prompt, decode_batches, names):
+    """measure(model, vocab, rng) for a model on the step engine: whole-prompt prefill (CUDA events, L2 flushed between
+    repetitions), the same prompt in two portions, decode steps at context prompt / 8, and per-op times of one prefill and one
+    decode step (events around every kernel wrapper in `names` and every library product)."""
+    from mistralrs_b200 import engine, seq_ops as K
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=steps):
+        for _ in range(warmup):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+        return sorted(ts)[len(ts) // 2]
+
+    def by_op(fn):
+        acc, saved = {}, {}
+
+        def wrap(mod, name):
+            f = getattr(mod, name)
+
+            def g(*a, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = f(*a, **k)
+                e1.record()
+                acc.setdefault(name, []).append((e0, e1))
+                return r
+            setattr(mod, name, g)
+            saved[(mod, name)] = f
+        for n in names:
+            wrap(K, n)
+        wrap(torch, "bmm")
+        wrap(torch, "mm")
+        wrap(torch.nn.functional, "linear")      # every projection: mixers.linear and the biased ones call it
+        try:
+            torch.cuda.synchronize()
+            flush.zero_()
+            fn()
+            torch.cuda.synchronize()
+        finally:
+            for (mod, name), f in saved.items():
+                setattr(mod, name, f)
+        return {n: round(sum(a.elapsed_time(b) for a, b in v), 4) for n, v in acc.items()}
+
+    def measure(model, vocab, rng):
+        row = {}
+        eng = engine.Engine(model, max_tokens=max(prompt, 32 * (prompt // 8 + 64)) + 64, max_seqs=max(decode_batches))
+        toks = rng.integers(0, vocab, prompt).tolist()
+
+        def prefill():
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt)])
+            eng.finish(r)
+        t = timed(prefill)
+        row["prefill_tok_s"], row["prefill_ms"] = prompt / t, t * 1e3
+        row["prefill_ms_by_op"] = by_op(prefill)
+
+        def prefill_cut():                                   # the same prompt in two steps: the second portion continues the sequence
+            r = eng.new_request(toks)
+            eng.execute([(r, prompt // 2)])
+            eng.execute([(r, prompt - prompt // 2)])
+            eng.finish(r)
+        row["prefill_two_portions_ms"] = timed(prefill_cut) * 1e3
+        row["decode"] = []
+        ctx = prompt // 8
+        for b in decode_batches:
+            reqs = [eng.new_request(rng.integers(0, vocab, ctx + 64).tolist()) for _ in range(b)]
+            eng.execute([(r, ctx) for r in reqs])
+
+            def dec():
+                eng.execute([(r, 1) for r in reqs])
+            t = timed(dec, reps=max(steps, 5))
+            eng.decode_graphs, graphs = False, eng.decode_graphs          # the per-op table needs the eager step
+            ops = by_op(dec)
+            eng.decode_graphs = graphs
+            row["decode"].append({"batch": b, "context": ctx, "tok_s": b / t, "ms_per_step": t * 1e3, "graph": b in eng._graphs, "ms_by_op": ops})
+            for r in reqs:
+                eng.finish(r)
+        del eng
+        torch.cuda.empty_cache()
+        return row
+    return measure
+
+
+def bench_kibotar(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), prompt=4096, decode_batches=(1, 32)):
+    """Prefill and decode throughput of the Kibotar design through `engine.Engine.execute` at layer sizes of a real model, and
+    of the Fosulix design (the closest model: one f32 residual with RMS norms, latent attention over one cached row per token,
+    a linear recurrence with a decay per state row on the same scan, an input convolution, same engine and kernel library) at
+    equal width / depth / head sizes; then, per kernel, the achieved fraction of the measured HBM rate (or f32 / tensor
+    TFLOP/s) beside the like kernel of Fosulix.  CUDA events, L2 flushed between repetitions."""
+    import numpy as np
+    from mistralrs_b200 import fosulix, kibotar
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    tpeak = peaks.get("bf16_tflops_sustained", 1400.0)
+    warmup, steps = max(3, warmup), max(1, steps)
+    names = ["embed_scaled", "embed_pair", "streams_read_norm", "rms_residual", "glu_split", "gated_group_norm", "causal_conv", "linear_scan",
+             "activate_cols", "bounded_gate", "power_gate", "latent_prepare", "rotate_pairs", "latent_prompt_attention", "paged_attention",
+             "prompt_attention", "attention_prepare", "rotation_table", "pool_blocks", "mix_heads", "gate_cols", "moe_route_scored", "moe_small",
+             "moe_sort", "moe_gather", "moe_combine", "scale_rows"]
+    measure = engine_bench_tools(torch, dev, steps, warmup, prompt, decode_batches, names)
+    out = {"metric": "kibotar_prefill_tok_s", "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True,
+           "dtype": "bf16 (f32 residual, states, decays, norms, softmax and mixed weights)", "data": "synthetic", "sizes": []}
+    for width in widths:
+        rng = np.random.default_rng(width)
+        cj = kibotar_bench_config(width)
+        cfg = kibotar.KibotarConfig(cj)
+        model = kibotar.KibotarModel.random(cfg, dev, torch.bfloat16, seed=width, decay_rank=64)
+        row = {"width": width, "layers": len(cj["layers"]), "prompt_tokens": prompt}
+        row.update(measure(model, cfg.vocab, rng))
+        del model
+        torch.cuda.empty_cache()
+        fcj = fosulix_bench_config(width)
+        fcfg = fosulix.FosulixConfig(fcj)
+        fmodel = fosulix.FosulixModel.random(fcfg, dev, torch.bfloat16, seed=width)
+        row["fosulix_equal_size"] = near = measure(fmodel, fcfg.vocab, rng)
+        del fmodel
+        torch.cuda.empty_cache()
+        # ---- per kernel: achieved rate on the algorithmic bytes / flops of the prefill, beside the like kernel ----
+        T, W, H, d = prompt, width, width // 128, 128
+        att, lat = cj["layers"][1]["mixer"], cj["layers"][0]["mixer"]
+        G, win, pool, R = att["kv_heads"], att["mask"]["size"], att["mask"]["pool"], lat["kv_rank"]
+        flat = fcj["layers"][0]["mixer"]
+        fR, fdr, fqr, fwin = flat["kv_rank"], flat["rot_dim"], flat["q_rank"], flat["mask"]["size"]
+        ops, fops = row["prefill_ms_by_op"], near["prefill_ms_by_op"]
+        gbs = lambda nbytes, ms: nbytes / (ms * 1e-3) / 1e9 / hbm if ms else None
+        tfl = lambda flop, ms: flop / (ms * 1e-3) / 1e12 if ms else None
+        roof = {}
+        # residual pass: source read + result written (f32), y read, next input written (bf16); eight passes and the first norm
+        res = 8 * T * W * (4 + 4 + 2 + 2) + T * W * (4 + 4 + 2)
+        fres = 8 * T * W * (4 + 4 + 2 + 2) + sum((i + 1) * T * W * 4 + T * W * 4 for i in range(4)) + T * W * (4 + 2)
+        roof["rms_residual (norm before and after)"] = {"ms": ops.get("rms_residual"), "hbm_frac": gbs(res, ops.get("rms_residual")), "like": "rms_residual (depth average)",
+                                                        "like_ms": fops.get("rms_residual"), "like_hbm_frac": gbs(fres, fops.get("rms_residual"))}
+        roof["causal_conv (token shift, 2 taps)"] = {"ms": ops.get("causal_conv"), "hbm_frac": gbs(4 * T * W * (2 + 2), ops.get("causal_conv")), "like": "causal_conv (4 taps)",
+                                                     "like_ms": fops.get("causal_conv"), "like_hbm_frac": gbs(4 * T * W * (2 + 2), fops.get("causal_conv"))}
+        roof["embed_pair"] = {"ms": ops.get("embed_pair"), "hbm_frac": gbs(T * W * (2 + 2 + 4), ops.get("embed_pair")), "like": "embed_scaled",
+                              "like_ms": fops.get("embed_scaled"), "like_hbm_frac": gbs(T * W * (2 + 4), fops.get("embed_scaled"))}
+        prep = 2 * (T * 2 * R + T * 2 * R)                                  # two latent layers: latent columns read, cache row written
+        fprep = T * 2 * (2 * fqr + fR + fdr) + T * 2 * (fR + fdr) + 2 * T * 2 * fqr + 2 * T * H * fdr * 2 * 2
+        roof["latent_prepare"] = {"ms": ops.get("latent_prepare"), "hbm_frac": gbs(prep, ops.get("latent_prepare")), "like": "latent_prepare + rotate_pairs",
+                                  "like_ms": fops.get("latent_prepare", 0.0) + fops.get("rotate_pairs", 0.0),
+                                  "like_hbm_frac": gbs(fprep, fops.get("latent_prepare", 0.0) + fops.get("rotate_pairs", 0.0))}
+        lflop = 2 * 2.0 * H * (R + R) * (T * (T + 1) / 2)                   # two causal latent layers; per (query, key, head): dk + dv multiply-adds
+        fflop = 2 * 2.0 * H * ((fR + fdr) + fR) * sum(min(i + 1, fwin) for i in range(T))
+        roof["latent_prompt_attention (causal)"] = {"ms": ops.get("latent_prompt_attention"), "tflops": tfl(lflop, ops.get("latent_prompt_attention")),
+                                                    "tensor_frac": (tfl(lflop, ops.get("latent_prompt_attention")) or 0.0) / tpeak,
+                                                    "like": "latent_prompt_attention (window %d)" % fwin, "like_ms": fops.get("latent_prompt_attention"),
+                                                    "like_tflops": tfl(fflop, fops.get("latent_prompt_attention")),
+                                                    "like_tensor_frac": (tfl(fflop, fops.get("latent_prompt_attention")) or 0.0) / tpeak}
+        seen = sum(min(i + 1, win) + max(0, i - win + 1) // pool for i in range(T))
+        aflop = 2.0 * H * 2 * d * seen                                       # per (query, key, head): dk + dv multiply-adds
+        roof["prompt_attention (window + averaged blocks, once per value head)"] = {
+            "ms": ops.get("prompt_attention"), "value_heads": G, "tflops_executed": tfl(G * aflop, ops.get("prompt_attention")),
+            "tflops_needed": tfl(aflop, ops.get("prompt_attention")), "tensor_frac_executed": (tfl(G * aflop, ops.get("prompt_attention")) or 0.0) / tpeak,
+            "like": "latent_prompt_attention", "like_tflops": tfl(fflop, fops.get("latent_prompt_attention")),
+            "like_tensor_frac": (tfl(fflop, fops.get("latent_prompt_attention")) or 0.0) / tpeak}
+        aprep = T * 2 * (2 * H * d + 2 * G * d + 2 * G * d) + T * 2 * G * d * 2 + (T // pool) * (pool + 1) * 2 * G * d * 2
+        roof["attention_prepare + pool_blocks"] = {"ms": ops.get("attention_prepare", 0.0) + ops.get("pool_blocks", 0.0),
+                                                   "hbm_frac": gbs(aprep, ops.get("attention_prepare", 0.0) + ops.get("pool_blocks", 0.0)),
+                                                   "like": "latent_prepare + rotate_pairs",
+                                                   "like_hbm_frac": gbs(fprep, fops.get("latent_prepare", 0.0) + fops.get("rotate_pairs", 0.0))}
+        roof["mix_heads (+ output gate)"] = {"ms": ops.get("mix_heads"), "hbm_frac": gbs(T * H * G * d * 4 + T * H * d * (2 + 2), ops.get("mix_heads")),
+                                             "like": "gated_group_norm", "like_hbm_frac": gbs(2 * T * H * d * (4 + 2), fops.get("gated_group_norm"))}
+        roof["linear_scan (per-row decay, own keys)"] = {"ms": ops.get("linear_scan"), "tflops_f32": tfl(T * H * 5.0 * d * d, ops.get("linear_scan")),
+                                                         "like": "linear_scan (per-row decay, two layers)", "like_ms": fops.get("linear_scan"),
+                                                         "like_tflops_f32": tfl(2 * T * H * 5.0 * d * d, fops.get("linear_scan"))}
+        roof["power_gate"] = {"ms": ops.get("power_gate"), "hbm_frac": gbs(T * H * d * (2 + 4), ops.get("power_gate")), "like": "bounded_gate (two layers)",
+                              "like_ms": fops.get("bounded_gate"), "like_hbm_frac": gbs(2 * T * H * d * (2 + 4), fops.get("bounded_gate"))}
+        roof["gated_group_norm (per head, silu gate)"] = {"ms": ops.get("gated_group_norm"), "hbm_frac": gbs(T * H * d * (4 + 2 + 2), ops.get("gated_group_norm")),
+                                                          "like": "gated_group_norm (two layers, no gate)", "like_ms": fops.get("gated_group_norm"),
+                                                          "like_hbm_frac": gbs(2 * T * H * d * (4 + 2), fops.get("gated_group_norm"))}
+        roof["gate_cols (a gate per head)"] = {"ms": ops.get("gate_cols"), "hbm_frac": gbs(2 * T * H * d * (2 + 2), ops.get("gate_cols"))}
+        roof["activate_cols (squared relu)"] = {"ms": ops.get("activate_cols"), "hbm_frac": gbs(4 * T * 4 * W * (2 + 2), ops.get("activate_cols")), "like": "glu_split",
+                                                "like_ms": fops.get("glu_split"), "like_hbm_frac": gbs(4 * T * 2 * W * (2 * 2 + 2), fops.get("glu_split"))}
+        lib_ms = lambda o: o.get("linear", 0.0) + o.get("bmm", 0.0) + o.get("mm", 0.0)
+        roof["library products (linear + bmm + mm)"] = {"ms": lib_ms(ops), "like_ms": lib_ms(fops)}
+        for bi, b in enumerate(decode_batches):
+            dk = row["decode"][bi]["ms_by_op"], near["decode"][bi]["ms_by_op"]
+            ctx = prompt // 8
+            lbytes = 2 * b * ctx * R * 2                                      # two latent layers: the context's latent rows once per token
+            flbytes = 2 * b * min(ctx, fwin) * (fR + fdr) * 2
+            roof["latent_prompt_attention (decode, b=%d)" % b] = {"ms": dk[0].get("latent_prompt_attention"), "hbm_frac": gbs(lbytes, dk[0].get("latent_prompt_attention")),
+                                                                  "like": "latent_prompt_attention", "like_ms": dk[1].get("latent_prompt_attention"),
+                                                                  "like_hbm_frac": gbs(flbytes, dk[1].get("latent_prompt_attention"))}
+            abytes = b * min(ctx, win) * 2 * G * d * 2
+            roof["paged_attention (decode, every value head, b=%d)" % b] = {"ms": dk[0].get("paged_attention"), "hbm_frac": gbs(abytes, dk[0].get("paged_attention")),
+                                                                            "like": "latent_prompt_attention", "like_ms": dk[1].get("latent_prompt_attention"),
+                                                                            "like_hbm_frac": gbs(flbytes, dk[1].get("latent_prompt_attention"))}
+        row["roofline"] = roof
+        out["sizes"].append(row)
+    out["value"] = out["sizes"][0]["prefill_tok_s"]
+    out["ms_per_step"] = out["sizes"][0]["prefill_ms"]
+    out["config"] = {"workload": "4 layers (latent attention, attention over a window of 1024 plus averaged blocks of 8 with head-mixed weights, gated linear "
+                                 "attention, latent attention; dense feed-forwards of 4 x width), widths %s, %d-token prompt; decode at context %d; Fosulix at "
+                                 "equal sizes beside it; L2 flushed between repetitions" % (list(widths), prompt, prompt // 8)}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -965,11 +1187,12 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="headline workload: 1 = TinyLlama-1.1B Q4_K_M on the CPU (plumbing, no GPU), 2 = 8B Q4_K_M decode b=1 (default), "
                          "3 = 8B Q8_0 prefill 4096, 4 = Mistral-7B GPTQ b=32, 5 = Llama-3-70B Q4_K_M tensor parallel (needs --gpus 8)")
-    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun", "kilizen", "fosulix"],
+    ap.add_argument("--arch", default="llama", choices=["llama", "nisasun", "kilizen", "fosulix", "kibotar"],
                     help="nisasun: prefill / decode throughput of the Nisasun design on the step engine at layer sizes of a real model "
                          "(random weights), beside the Llama path at equal width / depth / feed-forward size, with a per-kernel table; "
                          "kilizen: the same for the Kilizen design, beside Nisasun at equal sizes; "
-                         "fosulix: the same for the Fosulix design, beside Kilizen at equal sizes")
+                         "fosulix: the same for the Fosulix design, beside Kilizen at equal sizes; "
+                         "kibotar: the same for the Kibotar design, beside Fosulix at equal sizes")
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model")
     ap.add_argument("--pdl", type=int, default=int(os.environ.get("MRS_PDL", "1")))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -1012,6 +1235,9 @@ def main():
         return
     if args.arch == "fosulix":
         print(json.dumps(bench_fosulix(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
+        return
+    if args.arch == "kibotar":
+        print(json.dumps(bench_kibotar(torch, dev, peaks, steps=args.steps, warmup=args.warmup)))
         return
     if args.config == 3 and world == 1:
         pf = bench_prefill_q8(M, torch, dev, peaks, layers=args.layers)

@@ -276,6 +276,13 @@ int mrs_seq_prompt_attention(const void *q, int64_t q_ld, const void *k_cache, c
                              const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
                              int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
                              const float *sink, int64_t stream);
+/* The same with averaged blocks before the window (pool > 0, rows pool_base.. of the caches as for mrs_seq_paged_attention;
+ * needs window > 0 and keep_first 0) and / or with every head's weights applied to every value head (every_value_head != 0:
+ * out is then f32 [n_tok, heads, kv_heads * d] with row stride out_ld floats — the input of mrs_seq_mix_heads). */
+int mrs_seq_prompt_attention_pooled(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, void *out, int64_t out_ld,
+                                    const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
+                                    int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
+                                    const float *sink, int pool, int64_t pool_base, int every_value_head, int64_t stream);
 /* ---- attention through a shared latent ----------------------------------------------------------------- */
 /* Per token, from the columns of one projection y (row stride y_ld, activation type), any part optional:
  *   q_out[t] = rms_norm(y[t][q_col : q_col + q_rank]) * q_norm_w                      (the query latent, activation type)

@@ -8,6 +8,13 @@
 // shared-memory ring (cp.async, 16 bytes at a time, the page looked up per row), S = QK^T and O = PV as m16n8k16 MMAs
 // with f32 accumulation, online softmax in f32 on a base-2 exponent.  The key tiles of a query tile are the kept first
 // tiles followed by the window's tiles; the denominator ends with the sink's term.
+//
+// Two further forms of the same loop.  Averaged blocks (pool > 0): instead of kept first keys, the tiles before the window
+// hold one averaged key / value row per block of `pool` positions (rows pool_base.. of the same cache tensors, see
+// window_attn.cu's key_row); entry b is visible to a query at position i when the block ends at or before i - window.
+// Every value head (v_heads > 1): grid.y runs over (value head, query head) pairs — the head's own keys, the given value
+// head's values — and the result goes to an f32 matrix [tokens, heads, v_heads * D]; a mixing of softmax weights across
+// heads is then a weighted sum of these rows (pooled.cu's mix_heads).
 #include "../mma_common.cuh"
 
 #include "../../../include/mrs_b200_seq.h"
@@ -28,6 +35,10 @@ struct Params {
   float scale_log2;
   int window, keep_first;      // window <= 0: every earlier position
   const float *sink;
+  int pool, per_page;          // pool > 0: averaged blocks before the window; per_page = ceil(page_size / pool)
+  int64_t pool_base;
+  int v_heads;                 // 1, or the number of value heads when every head is applied to every value head
+  int o_f32;                   // the result is f32 [tokens, heads, v_heads * D] (o is then float *)
 };
 
 template <int D>
@@ -39,7 +50,8 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
   uint8_t *sv[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z, h = blockIdx.y, kvh = h / (p.H / p.KVH);
+  const int b = blockIdx.z, h = blockIdx.y % p.H, vsel = blockIdx.y / p.H, kvh = h / (p.H / p.KVH);
+  const int vh = p.v_heads > 1 ? vsel : kvh;        // the value head this CTA applies the head's weights to
   const int seq0 = p.portions[4 * b], len = p.portions[4 * b + 1], past = p.portions[4 * b + 2];
   const int32_t *table = p.pages + (int64_t)p.portions[4 * b + 3] * p.pages_ld;
   const int total = past + len;                     // positions the sequence holds after this step
@@ -49,11 +61,13 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
   const int q0 = qt * BM;                           // row inside the portion; its position is past + row
   const T *qg = p.q + (int64_t)seq0 * p.q_ld + (int64_t)h * D;
   T *og = p.o + (int64_t)seq0 * p.o_ld + (int64_t)h * D;
+  float *ogf = (float *)p.o + (int64_t)seq0 * p.o_ld + ((int64_t)h * p.v_heads + vsel) * D;
 
   // key tiles of this query tile: the kept first positions that lie before the window's first tile, then the window
   const int kv_end = min(total, past + q0 + BM);
   const int win_begin = p.window > 0 ? max(0, past + q0 - p.window + 1) / BN * BN : 0;
-  const int kept_end = min(p.keep_first, win_begin);
+  // entries before the window: kept first positions, or averaged blocks (as many as the tile's last query sees)
+  const int kept_end = p.pool > 0 ? max(0, kv_end - p.window) / p.pool : min(p.keep_first, win_begin);
   const int kept_tiles = (kept_end + BN - 1) / BN;                  // kept_tiles * BN <= win_begin: no key twice
   const int nt = kept_tiles + (kv_end - win_begin + BN - 1) / BN;
   auto tile_start = [&](int t) { return t < kept_tiles ? t * BN : win_begin + (t - kept_tiles) * BN; };
@@ -63,11 +77,18 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
     for (int c = tid; c < BN * CPR; c += THREADS) {
       const int row = c / CPR, ch = c % CPR;
       const int j = t0 + row;
-      const bool ok = j < kv_end;
+      const bool averaged = p.pool > 0 && t < kept_tiles;
+      const bool ok = j < (averaged ? kept_end : kv_end);
       const int jj = ok ? j : 0;
-      const int64_t at = (((int64_t)table[jj / p.page_size] * p.page_size + jj % p.page_size) * p.KVH + kvh) * D + ch * 8;
-      cp_async16(sk[buf] + tile_off<D>(row, ch), p.k_cache + at, ok);
-      cp_async16(sv[buf] + tile_off<D>(row, ch), p.v_cache + at, ok);
+      int64_t slot;
+      if (averaged) {
+        const int page = (jj * p.pool) / p.page_size, first = (page * p.page_size + p.pool - 1) / p.pool;
+        slot = p.pool_base + (int64_t)table[page] * p.per_page + (jj - first);
+      } else {
+        slot = (int64_t)table[jj / p.page_size] * p.page_size + jj % p.page_size;
+      }
+      cp_async16(sk[buf] + tile_off<D>(row, ch), p.k_cache + (slot * p.KVH + kvh) * D + ch * 8, ok);
+      cp_async16(sv[buf] + tile_off<D>(row, ch), p.v_cache + (slot * p.KVH + vh) * D + ch * 8, ok);
     }
     cp_async_commit();
   };
@@ -130,7 +151,9 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
         if (need_mask) {
           const int col = t0 + 8 * j + 2 * (lane & 3) + (e & 1);
           const int row = past + row_a + ((e >> 1) << 3);          // the query's position
-          const bool ok = col < total && col <= row && (p.window <= 0 || row - col < p.window || col < p.keep_first);
+          bool ok;
+          if (p.pool > 0 && t < kept_tiles) ok = (col + 1) * p.pool - 1 <= row - p.window;        // the block ends at or before row - window
+          else ok = col < total && col <= row && (p.window <= 0 || row - col < p.window || col < p.keep_first);
           if (!ok) s = -INFINITY;
         }
         sacc[j][e] = s;
@@ -191,6 +214,11 @@ __global__ void __launch_bounds__(THREADS, 1) prompt_attention_kernel(const Para
 #pragma unroll
   for (int i = 0; i < DT; i++) {
     const int col = 8 * i + 2 * (lane & 3);
+    if (p.o_f32) {
+      if (row_a < len) *(float2 *)(ogf + (int64_t)row_a * p.o_ld + col) = make_float2(oacc[i][0] * inv0, oacc[i][1] * inv0);
+      if (row_a + 8 < len) *(float2 *)(ogf + (int64_t)(row_a + 8) * p.o_ld + col) = make_float2(oacc[i][2] * inv1, oacc[i][3] * inv1);
+      continue;
+    }
     if (row_a < len) *(uint32_t *)(og + (int64_t)row_a * p.o_ld + col) = pack2<T>(oacc[i][0] * inv0, oacc[i][1] * inv0);
     if (row_a + 8 < len) *(uint32_t *)(og + (int64_t)(row_a + 8) * p.o_ld + col) = pack2<T>(oacc[i][2] * inv1, oacc[i][3] * inv1);
   }
@@ -206,7 +234,7 @@ static int launch(const Params &p, int n, int longest, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     raised = true;
   }
-  kern<<<dim3((longest + BM - 1) / BM, p.H, n), THREADS, bytes, st>>>(p);
+  kern<<<dim3((longest + BM - 1) / BM, p.H * p.v_heads, n), THREADS, bytes, st>>>(p);
   return (int)cudaGetLastError();
 }
 
@@ -216,8 +244,18 @@ extern "C" int mrs_seq_prompt_attention(const void *q, int64_t q_ld, const void 
                                         const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
                                         int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
                                         const float *sink, int64_t stream) {
+  return mrs_seq_prompt_attention_pooled(q, q_ld, k_cache, v_cache, out, out_ld, portions, n_portions, longest, pages, pages_ld, page_size, heads,
+                                         kv_heads, d, scale, window, keep_first, sink, 0, 0, 0, stream);
+}
+
+extern "C" int mrs_seq_prompt_attention_pooled(const void *q, int64_t q_ld, const void *k_cache, const void *v_cache, void *out, int64_t out_ld,
+                                               const int32_t *portions, int n_portions, int longest, const int32_t *pages, int pages_ld,
+                                               int page_size, int heads, int kv_heads, int d, float scale, int window, int keep_first,
+                                               const float *sink, int pool, int64_t pool_base, int every_value_head, int64_t stream) {
   if (n_portions <= 0 || longest <= 0) return 0;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || (d != 64 && d != 128) || !portions || !pages || page_size <= 0) return -2;
+  if (pool > 0 && (window <= 0 || keep_first > 0)) return -2;
+  if ((int64_t)heads * (every_value_head ? kv_heads : 1) > 65535) return -2;
   if ((q_ld | out_ld) % 8 || (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)) return -3;
   seqp::Params p = {};
   p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
@@ -226,5 +264,8 @@ extern "C" int mrs_seq_prompt_attention(const void *q, int64_t q_ld, const void 
   p.H = heads; p.KVH = kv_heads; p.q_ld = q_ld; p.o_ld = out_ld;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.keep_first = keep_first > 0 ? keep_first : 0; p.sink = sink;
+  p.pool = pool > 0 ? pool : 0; p.per_page = pool > 0 ? (page_size + pool - 1) / pool : 0; p.pool_base = pool_base;
+  p.v_heads = every_value_head ? kv_heads : 1;
+  p.o_f32 = every_value_head ? 1 : 0;
   return d == 128 ? seqp::launch<128>(p, n_portions, longest, (cudaStream_t)stream) : seqp::launch<64>(p, n_portions, longest, (cudaStream_t)stream);
 }

@@ -177,17 +177,34 @@ class WindowAttention:
             K.gate_cols(out[:, out_col:], y, gate_col, self.heads * self.dv, 1, gate_act)
 
     def _attend_general(self, y, col0, batch, cache, page_size, out, out_col, out_scale, gate_col, gate_act):
+        """Averaged blocks and / or mixed heads.  Long portions take the sequence library's tensor-core prompt kernel when they
+        fit (bf16, equal head sizes of 64 or 128, aligned rows) — with mixed heads once per value head, every head's weights on
+        that head's values; every other token takes the (token, head) kernel, which reads a row's value heads side by side."""
         H, G, dv = self.heads, self.kv_heads, self.dv
-        if self.talk is None:
-            K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, dv, self.scale, self.window, self.keep_first, self.sink, batch,
-                              page_size, out, out_col, out_scale, pool=self.pool, pool_base=self.pool_base)
-            if gate_col is not None:
-                K.gate_cols(out[:, out_col:], y, gate_col, H * dv, 1, gate_act)
-            return
-        every = torch.empty(y.shape[0], H * G * dv, dtype=torch.float32, device=y.device)      # head g's weights on every value head
-        K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, G * dv, self.scale, self.window, self.keep_first, self.sink, batch,
-                          page_size, every, 0, out_scale, v_row=G * dv, pool=self.pool, pool_base=self.pool_base, v_shared=True)
-        K.mix_heads(every, self.talk, H, G, dv, out[:, out_col:], y if gate_col is not None else None, gate_col or 0, gate_act)
+        mixed = self.talk is not None
+        res = torch.empty(y.shape[0], H * G * dv, dtype=torch.float32, device=y.device) if mixed else out      # mixed: head g's weights on every value head
+        res_col = 0 if mixed else out_col
+        tok_index = None
+        fits = y.dtype == torch.bfloat16 and self.dk == dv and dv in (64, 128) and not self.values_from_keys and \
+            all(v % 8 == 0 for v in (y.stride(0), col0, res.stride(0), res_col))
+        if batch.long and fits:
+            K.prompt_attention(y, col0, cache["k"], cache["v"], batch, page_size, H, G, dv, self.scale, self.window, self.keep_first, self.sink, res,
+                               res_col, pool=self.pool, pool_base=self.pool_base, every_value_head=mixed)
+            if out_scale != 1.0:
+                for row0, rows, _, _ in batch.long:
+                    K.scale_rows(res, row0, rows, res_col, res.shape[1] if mixed else H * dv, out_scale)
+            tok_index = batch.short_tok
+        if tok_index is None or tok_index.numel() > 0:
+            if mixed:
+                K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, G * dv, self.scale, self.window, self.keep_first, self.sink, batch,
+                                  page_size, res, 0, out_scale, tok_index, v_row=G * dv, pool=self.pool, pool_base=self.pool_base, v_shared=True)
+            else:
+                K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, dv, self.scale, self.window, self.keep_first, self.sink, batch,
+                                  page_size, out, out_col, out_scale, tok_index, pool=self.pool, pool_base=self.pool_base)
+        if mixed:
+            K.mix_heads(res, self.talk, H, G, dv, out[:, out_col:], y if gate_col is not None else None, gate_col or 0, gate_act)
+        elif gate_col is not None:
+            K.gate_cols(out[:, out_col:], y, gate_col, H * dv, 1, gate_act)
 
     def _attend_plain(self, y, col0, kc, vc, batch, cache, page_size, out, out_col, out_scale):
         tok_index = None

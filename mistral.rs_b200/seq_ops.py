@@ -452,13 +452,16 @@ def gate_cols(x, gate, gate_col, cols, group, act):
                                 _i(act), _i(x.shape[0]), _st(x)), "gate_cols")
 
 
-def prompt_attention(y, q_col, k_cache, v_cache, batch, page_size, heads, kv_heads, d, scale, window, keep_first, sink, out, out_col=0):
+def prompt_attention(y, q_col, k_cache, v_cache, batch, page_size, heads, kv_heads, d, scale, window, keep_first, sink, out, out_col=0, pool=0,
+                     pool_base=0, every_value_head=False):
     """The long portions of the step (batch.long: fresh or continued) on tensor cores: queries from their rows of y, keys
-    and values from the pages (bf16, head size 64 or 128)."""
-    _ok(lib().mrs_seq_prompt_attention(_p(y, q_col), _l(y.stride(0)), _p(k_cache), _p(v_cache), _p(out, out_col), _l(out.stride(0)),
-                                       _p(batch.long_rows), _i(len(batch.long)), _i(max(n for _, n, _, _ in batch.long)), _p(batch.pages),
-                                       _i(batch.pages.shape[1]), _i(page_size), _i(heads), _i(kv_heads), _i(d), _f(scale), _i(int(window)),
-                                       _i(int(keep_first)), _p(sink), _st(y)), "prompt_attention")
+    and values from the pages (bf16, head size 64 or 128).  pool / pool_base: averaged blocks before the window, as for
+    `paged_attention`.  every_value_head: `out` is f32 [T, heads * kv_heads * d], every head's weights on every value head."""
+    _ok(lib().mrs_seq_prompt_attention_pooled(_p(y, q_col), _l(y.stride(0)), _p(k_cache), _p(v_cache), _p(out, out_col), _l(out.stride(0)),
+                                              _p(batch.long_rows), _i(len(batch.long)), _i(max(n for _, n, _, _ in batch.long)), _p(batch.pages),
+                                              _i(batch.pages.shape[1]), _i(page_size), _i(heads), _i(kv_heads), _i(d), _f(scale), _i(int(window)),
+                                              _i(int(keep_first)), _p(sink), _i(int(pool)), _l(int(pool_base)), _i(int(bool(every_value_head))),
+                                              _st(y)), "prompt_attention")
 
 
 # ---- stabilised matrix memory ---------------------------------------------------------------------------

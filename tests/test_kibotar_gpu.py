@@ -255,6 +255,56 @@ def test_attention_other_sizes(cuda, layer):
     close_rows(got, want, 3e-5)
 
 
+TC_LAYERS = [attn_layer(heads=4, kv_heads=2, dim=64, vdim=64, window=70, pool=8, rot_dims=32),
+             attn_layer(heads=3, kv_heads=1, dim=128, vdim=128, window=64, pool=16, rot_dims=64),
+             attn_layer(heads=8, kv_heads=4, dim=64, vdim=64, window=200, pool=5, rot_dims=64, scaling=None),
+             attn_layer(heads=2, kv_heads=2, dim=64, vdim=64, window=33, pool=1, rot_dims=16)]
+
+
+@pytest.mark.parametrize("layer", TC_LAYERS)
+@pytest.mark.parametrize("portions", [[300], [70, 33, 1, 196], [31, 269]])
+def test_attention_tensor_core_kernel(cuda, layer, portions):
+    """bf16 portions of 32 tokens or more run on the tensor-core prompt kernel, once per value head: fresh and continued
+    portions, windows and averaged blocks inside and across its key tiles, one / some / all heads sharing a value head."""
+    got, want = mixer_case(cuda, layer, torch.bfloat16, sum(portions), portions)
+    close_rows(got, want, 3e-2)
+
+
+def test_averaged_blocks_without_head_mixing(cuda):
+    """The mechanisms are separate: a layer with averaged blocks but no mixing matrix (identity in the plain model), on the
+    (token, head) kernel in f32 and on tensor cores in bf16."""
+    for dtype, tol, layer in ((torch.float32, 3e-5, attn_layer(pool=4)), (torch.bfloat16, 3e-2, TC_LAYERS[0])):
+        cj = make_cfg([layer])
+        model, w = build(cj, dtype, cuda, 3)
+        mixer = model.layers[0].mixer
+        mixer.attn.talk = None
+        w["l0.mix.talk"] = torch.eye(layer["mixer"]["heads"], dtype=F64)
+        h = torch.randn(150, 72, generator=torch.Generator().manual_seed(3)).to(dtype)
+        cache = mixer.alloc_cache(1, 16 * 20, dtype, cuda)
+        got, at = [], 0
+        for n in (90, 1, 59):
+            got.append(mixer.forward(h[at:at + n].to(cuda).contiguous(), seq_batch(cuda, [(n, at, 0, 2)]), cache).double().cpu())
+            at += n
+        close_rows(torch.cat(got), plain_mixer(layer, h.double(), w, 1e-5), tol)
+
+
+def test_tensor_core_kernel_takes_several_sequences(cuda):
+    """Two sequences start in one step beside a long portion that continues a third and a single decoded token of a fourth."""
+    layer = TC_LAYERS[0]
+    cj = make_cfg([layer], width=64)
+    model, w = build(cj, torch.bfloat16, cuda, 7)
+    mixer = model.layers[0].mixer
+    cache = mixer.alloc_cache(4, 16 * 60, torch.bfloat16, cuda)
+    g = torch.Generator().manual_seed(7)
+    hs = [torch.randn(n, 64, generator=g).to(torch.bfloat16) for n in (150, 33, 130, 12)]
+    mixer.forward(torch.cat([hs[2][:90], hs[3][:11]]).to(cuda).contiguous(), seq_batch(cuda, [(90, 0, 2, 30), (11, 0, 3, 40)]), cache)
+    b = seq_batch(cuda, [(150, 0, 0, 1), (40, 90, 2, 30), (1, 11, 3, 40), (33, 0, 1, 12)])
+    assert len(b.long) == 3 and b.short_tok.numel() == 1
+    got = mixer.forward(torch.cat([hs[0], hs[2][90:], hs[3][11:], hs[1]]).to(cuda).contiguous(), b, cache).double().cpu()
+    want = [plain_mixer(layer, h.double(), w, 1e-5) for h in hs]
+    close_rows(got, torch.cat([want[0], want[2][90:], want[3][11:], want[1]]), 3e-2)
+
+
 @pytest.mark.parametrize("page_size,pool", [(4, 3), (4, 8), (16, 5), (32, 12), (8, 8)])
 def test_averaged_blocks_across_pages(cuda, page_size, pool):
     """Blocks that straddle pages, span several pages, or fill one exactly; the pages of the sequence are not the first of the pool."""
@@ -325,7 +375,7 @@ def pointed_attention_edit(width, dk, dv, heads, kv_heads, rot=False):
         t["l0.mix.q"].copy_(eye(dk, width).repeat(heads, 1).to(torch.bfloat16))
         t["l0.mix.k"].copy_(eye(dk, width).repeat(kv_heads, 1).to(torch.bfloat16))
         t["l0.mix.v"].copy_(eye(dv, width, dk).repeat(kv_heads, 1).to(torch.bfloat16))
-        for b in ("q.b", "k.b", "v.b"):
+        for b in ("q.b", "k.b", "v.b", "o.b"):
             t["l0.mix." + b].zero_()
         t["l0.mix.g"].zero_()
         t["l0.mix.g"][:, -1] = 8.0
@@ -345,21 +395,26 @@ def pointed_inputs(T, width, dk, target, seed, gain=3.0):
     return h
 
 
+# the same edges on the (token, head) kernel in f32 and, with heads of 64, on the tensor-core prompt kernel in bf16
+EDGE_KINDS = [(torch.float32, 3e-5, 16, 24, 64), (torch.bfloat16, 3e-2, 64, 64, 136)]
+
+
 @pytest.mark.parametrize("distance", [-2, -1, 0, 1])
 @pytest.mark.parametrize("decoded", [False, True])
-def test_window_edge_shows(cuda, distance, decoded):
+@pytest.mark.parametrize("dtype,tol,dk,dv,width", EDGE_KINDS, ids=["f32", "bf16-tensor-cores"])
+def test_window_edge_shows(cuda, distance, decoded, dtype, tol, dk, dv, width):
     """One earlier token shares the last query's direction under a large score scale; it sits around the window's far edge, and
     one step outside it is gone (its block is not yet whole).  The blocks are long, so no averaged entry hides the edge."""
-    window, T, dk = 24, 120, 16
+    window, T = 24, 120
     target = T - 1 - (window - 1) - distance                   # distance <= 0: in sight
-    layer = attn_layer(heads=4, kv_heads=2, dim=dk, vdim=24, window=window, pool=64, rot_dims=0, scale=1.0)
+    layer = attn_layer(heads=4, kv_heads=2, dim=dk, vdim=dv, window=window, pool=64, rot_dims=0, scale=16.0 / dk)
     layer["mixer"].pop("rot")
-    h = pointed_inputs(T, 64, dk, target, 9)
+    h = pointed_inputs(T, width, dk, target, 9).to(dtype).float()
     cuts = [T - 3, 1, 1, 1] if decoded else [T]
-    got, want = mixer_case(cuda, layer, torch.float32, T, cuts, seed=9, edit=pointed_attention_edit(64, dk, 24, 4, 2), width=64, h=h)
-    close_rows(got, want, 3e-5)
-    cj = make_cfg([layer], width=64)
-    _, w = build(cj, torch.float32, cuda, 9, edit=pointed_attention_edit(64, dk, 24, 4, 2))
+    got, want = mixer_case(cuda, layer, dtype, T, cuts, seed=9, edit=pointed_attention_edit(width, dk, dv, 4, 2), width=width, h=h)
+    close_rows(got, want, tol)
+    cj = make_cfg([layer], width=width)
+    _, w = build(cj, torch.float32, cuda, 9, edit=pointed_attention_edit(width, dk, dv, 4, 2))
     other = copy.deepcopy(layer)
     other["mixer"]["mask"]["size"] = window + distance if distance > 0 else window - 1 + distance
     assert (plain_mixer(other, h.double(), w, 1e-5)[-1] - want[-1]).norm() > 0.2 * want[-1].norm()
@@ -368,24 +423,25 @@ def test_window_edge_shows(cuda, distance, decoded):
 @pytest.mark.parametrize("missing", [0, 1])
 @pytest.mark.parametrize("decoded", [False, True])
 @pytest.mark.parametrize("pool", [4, 6])
-def test_block_edge_shows(cuda, pool, missing, decoded):
+@pytest.mark.parametrize("dtype,tol,dk,dv,width", EDGE_KINDS, ids=["f32", "bf16-tensor-cores"])
+def test_block_edge_shows(cuda, pool, missing, decoded, dtype, tol, dk, dv, width):
     """The matching token lies in the newest block before the window.  missing 0: the block's last position has just left the
     window, so its average is seen; missing 1: one of its positions is still inside the window's reach of exclusion — the
     block is not whole yet and the token is seen neither singly nor averaged."""
-    window, dk = 10, 16
+    window = 10
     nb = 7
     T = nb * pool + window - missing                            # the last query, position T - 1, sees a block that ends at or before T - 1 - window
     target = nb * pool - pool + 1                               # inside block nb - 1
-    layer = attn_layer(heads=4, kv_heads=2, dim=dk, vdim=24, window=window, pool=pool, rot_dims=0, scale=1.0)
+    layer = attn_layer(heads=4, kv_heads=2, dim=dk, vdim=dv, window=window, pool=pool, rot_dims=0, scale=16.0 / dk)
     layer["mixer"].pop("rot")
-    h = pointed_inputs(T, 64, dk, target, 5, gain=3.0 * pool)
+    h = pointed_inputs(T, width, dk, target, 5, gain=3.0 * pool).to(dtype).float()
     cuts = [T - 3, 1, 1, 1] if decoded else [T]
-    got, want = mixer_case(cuda, layer, torch.float32, T, cuts, seed=5, edit=pointed_attention_edit(64, dk, 24, 4, 2), width=64, h=h)
-    close_rows(got, want, 3e-5)
+    got, want = mixer_case(cuda, layer, dtype, T, cuts, seed=5, edit=pointed_attention_edit(width, dk, dv, 4, 2), width=width, h=h)
+    close_rows(got, want, tol)
     seen_blocks, lo = P.pooled_window_keys(T - 1, window, pool)
     assert seen_blocks == (nb if missing == 0 else nb - 1) and lo > target
-    cj = make_cfg([layer], width=64)
-    _, w = build(cj, torch.float32, cuda, 5, edit=pointed_attention_edit(64, dk, 24, 4, 2))
+    cj = make_cfg([layer], width=width)
+    _, w = build(cj, torch.float32, cuda, 5, edit=pointed_attention_edit(width, dk, dv, 4, 2))
     other = copy.deepcopy(layer)
     other["mixer"]["mask"]["size"] = window + (1 if missing == 0 else -1)       # one wider hides the block, one narrower shows it
     assert (plain_mixer(other, h.double(), w, 1e-5)[-1] - want[-1]).norm() > 0.2 * want[-1].norm()
@@ -582,6 +638,19 @@ def test_bfloat16_model(cuda):
     got = replay(eng, p, [[("a", 70), ("b", 5)], [("a", 1), ("b", 35)], [("a", 49)]])
     for k in p:
         assert_close(got[k], P.forward(FULL, w, p[k]).numpy(), torch.bfloat16, k)
+
+
+def test_bfloat16_model_on_tensor_cores(cuda):
+    """Heads of 64 and latents the tensor kernels take: long portions of several requests in one step, continued portions, decoded
+    tokens beside them."""
+    cj = make_cfg([attn_layer(heads=4, kv_heads=2, dim=64, vdim=64, window=40, pool=8, rot_dims=32, mlp=DENSE), gla_layer(mlp=None),
+                   latent_layer(heads=4, dim=24, vdim=40, kv_rank=64, mlp=DENSE)], width=64, loop=(0, 2, 2))
+    model, w = build(cj, torch.bfloat16, cuda, 19)
+    p = {"a": tokens(200, 131, 1), "b": tokens(90, 131, 2), "c": tokens(40, 131, 3)}
+    eng = engine.Engine(model, max_tokens=352, max_seqs=3)
+    got = replay(eng, p, [[("a", 100), ("b", 45)], [("a", 1), ("b", 44), ("c", 39)], [("a", 99), ("b", 1), ("c", 1)]])
+    for k in p:
+        assert_close(got[k], P.forward(cj, w, p[k]).numpy(), torch.bfloat16, k)
 
 
 def test_greedy_generation_through_the_scheduler(cuda):
