@@ -40,8 +40,9 @@ __global__ void pool_blocks_kernel(T *__restrict__ k_cache, T *__restrict__ v_ca
   }
 }
 
-// one CTA per token; thread per output entry (h, d); the mixing row of h and the token's `a` rows are read through L1
-template <typename T>
+// one CTA per token; a thread takes VEC neighbouring entries of one head (16-byte loads of the f32 rows when VEC is 4); the
+// mixing matrix sits in shared memory, the token's `a` rows come through L1
+template <typename T, int VEC>
 __global__ void mix_heads_kernel(const float *__restrict__ a, const float *__restrict__ mix, const T *__restrict__ gate, int64_t gate_ld,
                                  int gate_act, T *__restrict__ out, int64_t out_ld, int heads, int kv_heads, int dv) {
   extern __shared__ float m[];      // [heads][heads]
@@ -49,12 +50,30 @@ __global__ void mix_heads_kernel(const float *__restrict__ a, const float *__res
   __syncthreads();
   const int t = blockIdx.x, all = kv_heads * dv, per = heads / kv_heads;
   const float *at = a + (int64_t)t * heads * all;
-  for (int e = threadIdx.x; e < heads * dv; e += blockDim.x) {
+  for (int e = threadIdx.x * VEC; e < heads * dv; e += blockDim.x * VEC) {
     const int h = e / dv, d = e % dv, col = (h / per) * dv + d;
-    float s = 0.0f;
-    for (int g = 0; g < heads; g++) s = fmaf(m[h * heads + g], at[(int64_t)g * all + col], s);
-    if (gate) s *= apply_act(to_f32<T>(gate[(int64_t)t * gate_ld + e]), gate_act);
-    out[(int64_t)t * out_ld + e] = from_f32<T>(s);
+    float s[VEC];
+#pragma unroll
+    for (int x = 0; x < VEC; x++) s[x] = 0.0f;
+    for (int g = 0; g < heads; g++) {
+      const float w = m[h * heads + g];
+      if (VEC == 4) {
+        const float4 v = *(const float4 *)(at + (int64_t)g * all + col);
+        s[0] = fmaf(w, v.x, s[0]); s[1 % VEC] = fmaf(w, v.y, s[1 % VEC]); s[2 % VEC] = fmaf(w, v.z, s[2 % VEC]); s[3 % VEC] = fmaf(w, v.w, s[3 % VEC]);
+      } else {
+        s[0] = fmaf(w, at[(int64_t)g * all + col], s[0]);
+      }
+    }
+    if (gate) {
+      if (VEC == 4) {
+        const float4 gv = act4(load4<T>(gate + (int64_t)t * gate_ld + e), gate_act);
+        s[0] *= gv.x; s[1 % VEC] *= gv.y; s[2 % VEC] *= gv.z; s[3 % VEC] *= gv.w;
+      } else {
+        s[0] *= apply_act(to_f32<T>(gate[(int64_t)t * gate_ld + e]), gate_act);
+      }
+    }
+    if (VEC == 4) store4<T>(out + (int64_t)t * out_ld + e, make_float4(s[0], s[1 % VEC], s[2 % VEC], s[3 % VEC]));
+    else out[(int64_t)t * out_ld + e] = from_f32<T>(s[0]);
   }
 }
 
@@ -87,9 +106,16 @@ extern "C" int mrs_seq_mix_heads(const float *a, const float *mix, const void *g
                                  int dtype, int heads, int kv_heads, int dv, int n_tok, int64_t stream) {
   if (n_tok <= 0) return 0;
   if (!a || !mix || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dv <= 0 || heads > 96) return -2;
-  const int items = heads * dv, th = items >= 1024 ? 256 : (items >= 256 ? 128 : 64);
-  SEQ_DISPATCH_DTYPE(dtype, (mix_heads_kernel<T><<<n_tok, th, (size_t)heads * heads * sizeof(float), (cudaStream_t)stream>>>(
-                                a, mix, (const T *)gate, gate_ld, gate_act, (T *)out, out_ld, heads, kv_heads, dv)));
+  const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
+  auto al = [](const void *p, int by) { return ((uintptr_t)p % by) == 0; };
+  const bool vec = dv % 4 == 0 && al(a, 16) && al(out, 4 * elem) && out_ld % 4 == 0 && (!gate || (al(gate, 4 * elem) && gate_ld % 4 == 0));
+  const int items = vec ? heads * dv / 4 : heads * dv, th = items >= 1024 ? 256 : (items >= 256 ? 128 : 64);
+  const size_t bytes = (size_t)heads * heads * sizeof(float);
+  cudaStream_t st = (cudaStream_t)stream;
+  SEQ_DISPATCH_DTYPE(dtype, {
+    if (vec) mix_heads_kernel<T, 4><<<n_tok, th, bytes, st>>>(a, mix, (const T *)gate, gate_ld, gate_act, (T *)out, out_ld, heads, kv_heads, dv);
+    else mix_heads_kernel<T, 1><<<n_tok, th, bytes, st>>>(a, mix, (const T *)gate, gate_ld, gate_act, (T *)out, out_ld, heads, kv_heads, dv);
+  });
   return launch_status();
 }
 
