@@ -251,6 +251,8 @@ typedef struct {
   int v_shared;           /* != 0: every head reads value columns [0, dv) of a row, whatever its key/value head — with dv = all
                              value heads side by side, head h's weights are applied to every value head */
   int out_f32;            /* != 0: out is f32 whatever the activation type */
+  int64_t out_head;       /* elements between the heads of an output row; 0: dv.  With v_shared, a call may cover a column range of
+                             the value heads (v_cache advanced to it) and write the same range of every head's output */
 } mrs_seq_paged_attention_args;
 int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args, int64_t stream);
 /* Averaged cache entries for attention over pooled blocks: for every token of the step whose position ends a block of `pool`

@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
                                                                int pages_ld, int page_size, const int32_t *__restrict__ seq_of_tok,
                                                                const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index,
                                                                int n_tok, T *__restrict__ out, int64_t out_ld, float out_scale, int64_t k_row,
-                                                               int64_t v_row, int pool, int64_t pool_base, int v_shared, int out_f32) {
+                                                               int64_t v_row, int pool, int64_t pool_base, int v_shared, int out_f32, int64_t out_head) {
   extern __shared__ __align__(16) float qsm[];   // [warps][dk]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int64_t job = (int64_t)blockIdx.x * (blockDim.x >> 5) + wib;
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(128) window_attention_kernel(const T *__restri
   const float inv = out_scale / l;
 #pragma unroll
   for (int c = 0; c < MAX_VCOLS; c++)
-    if (c * 32 + lane < dv) store_out<T>(out, (int64_t)t * out_ld + h * dv + c * 32 + lane, acc[c] * inv, out_f32);
+    if (c * 32 + lane < dv) store_out<T>(out, (int64_t)t * out_ld + h * out_head + c * 32 + lane, acc[c] * inv, out_f32);
 }
 
 // The same computation laid out for speed when the head sizes allow vector loads (dk a multiple of 8 and dv even):
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
     const T *__restrict__ q, int64_t q_ld, const T *__restrict__ k_cache, const T *__restrict__ v_cache, int heads, int kv_heads, int dk, int dv,
     float scale, int window, int keep_first, const float *__restrict__ sink, const int32_t *__restrict__ pages, int pages_ld, int page_size,
     const int32_t *__restrict__ seq_of_tok, const int32_t *__restrict__ pos_of_tok, const int32_t *__restrict__ tok_index, T *__restrict__ out,
-    int64_t out_ld, float out_scale, int64_t k_row, int64_t v_row, int pool, int64_t pool_base, int v_shared, int out_f32) {
+    int64_t out_ld, float out_scale, int64_t k_row, int64_t v_row, int pool, int64_t pool_base, int v_shared, int out_f32, int64_t out_head) {
   extern __shared__ __align__(16) float sm[];   // q [dk] | per warp: m, l, acc [VPAIRS * 64]
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const int ti = blockIdx.x / heads, h = blockIdx.x % heads, t = tok_index ? tok_index[ti] : ti, g = h / (heads / kv_heads);
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(SPLIT * 32) window_attention_vec_kernel(
       const float mw = part[w * (2 + VPAIRS * 64)];
       if (mw != -INFINITY) o = fmaf(part[w * (2 + VPAIRS * 64) + 2 + c], expf(mw - mx), o);
     }
-    store_out<T>(out, (int64_t)t * out_ld + h * dv + c, o * inv, out_f32);
+    store_out<T>(out, (int64_t)t * out_ld + h * out_head + c, o * inv, out_f32);
   }
 }
 
@@ -337,6 +337,7 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
   cudaStream_t st = (cudaStream_t)stream;
   const int elem = dtype == MRS_SEQ_BF16 ? 2 : 4;
   const int64_t k_row = a.k_row > 0 ? a.k_row : (int64_t)kv_heads * dk, v_row = a.v_row > 0 ? a.v_row : (int64_t)kv_heads * dv;
+  const int64_t out_head = a.out_head > 0 ? a.out_head : dv;
   const bool vec = dk % (16 / elem) == 0 && dv % 2 == 0 && dv <= 512 && ((uintptr_t)a.k_cache % 16) == 0 && ((uintptr_t)a.v_cache % 8) == 0 &&
                    k_row % (16 / elem) == 0 && v_row % 2 == 0;
   if (vec) {
@@ -345,7 +346,7 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
   window_attention_vec_kernel<T, VP, SPLIT><<<(unsigned)n_tok * heads, SPLIT * 32, (dk + SPLIT * (2 + VP * 64)) * sizeof(float), st>>>( \
       (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink,  \
       a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row, pool,     \
-      a.pool_base, a.v_shared, a.out_f32)
+      a.pool_base, a.v_shared, a.out_f32, out_head)
     SEQ_DISPATCH_DTYPE(dtype, {
       if (dv <= 64) SEQ_ATTN_VEC(1);
       else if (dv <= 128) SEQ_ATTN_VEC(2);
@@ -361,7 +362,7 @@ extern "C" int mrs_seq_paged_attention(const mrs_seq_paged_attention_args *args,
   window_attention_kernel<T, VC><<<(unsigned)((jobs + warps - 1) / warps), warps * 32, warps * dk * sizeof(float), st>>>(  \
       (const T *)a.q, a.q_ld, (const T *)a.k_cache, (const T *)a.v_cache, heads, kv_heads, dk, dv, a.scale, a.window, keep_first, a.sink, \
       a.pages, a.pages_ld, a.page_size, a.seq_of_tok, a.pos_of_tok, a.tok_index, n_tok, (T *)a.out, a.out_ld, a.out_scale, k_row, v_row, pool, \
-      a.pool_base, a.v_shared, a.out_f32)
+      a.pool_base, a.v_shared, a.out_f32, out_head)
   SEQ_DISPATCH_DTYPE(dtype, {
     if (dv <= 64) SEQ_ATTN_LAUNCH(2);
     else if (dv <= 128) SEQ_ATTN_LAUNCH(4);

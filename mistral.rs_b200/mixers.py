@@ -195,9 +195,13 @@ class WindowAttention:
                     K.scale_rows(res, row0, rows, res_col, res.shape[1] if mixed else H * dv, out_scale)
             tok_index = batch.short_tok
         if tok_index is None or tok_index.numel() > 0:
-            if mixed:
-                K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, G * dv, self.scale, self.window, self.keep_first, self.sink, batch,
-                                  page_size, res, 0, out_scale, tok_index, v_row=G * dv, pool=self.pool, pool_base=self.pool_base, v_shared=True)
+            if mixed:          # as many value heads per launch as the kernel's vector path takes (512 value columns)
+                per_call = max(1, 512 // dv)
+                for g0 in range(0, G, per_call):
+                    n = min(per_call, G - g0)
+                    K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, n * dv, self.scale, self.window, self.keep_first, self.sink,
+                                      batch, page_size, res, g0 * dv, out_scale, tok_index, v_row=G * dv, pool=self.pool, pool_base=self.pool_base,
+                                      v_shared=True, v_col=g0 * dv, out_head=G * dv)
             else:
                 K.paged_attention(y, col0, cache["k"], cache["v"], H, G, self.dk, dv, self.scale, self.window, self.keep_first, self.sink, batch,
                                   page_size, out, out_col, out_scale, tok_index, pool=self.pool, pool_base=self.pool_base)

@@ -103,7 +103,7 @@ class PagedAttentionArgs(ctypes.Structure):
                 ("seq_of_tok", ctypes.c_void_p), ("pos_of_tok", ctypes.c_void_p), ("tok_index", ctypes.c_void_p), ("n_tok", ctypes.c_int),
                 ("out", ctypes.c_void_p), ("out_ld", ctypes.c_int64), ("out_scale", ctypes.c_float),
                 ("k_row", ctypes.c_int64), ("v_row", ctypes.c_int64), ("pool", ctypes.c_int), ("pool_base", ctypes.c_int64),
-                ("v_shared", ctypes.c_int), ("out_f32", ctypes.c_int)]
+                ("v_shared", ctypes.c_int), ("out_f32", ctypes.c_int), ("out_head", ctypes.c_int64)]
 
 
 SCAN_SEGMENT = 256                  # tokens per segment when a long portion is scanned as segments side by side
@@ -406,18 +406,19 @@ def attention_prepare(y, q_col, k_col, v_col, norm_mode, q_norm_w, k_norm_w, eps
 
 
 def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, window, keep_first, sink, batch, page_size, out, out_col=0,
-                    out_scale=1.0, tok_index=None, k_row=0, v_row=0, pool=0, pool_base=0, v_shared=False):
+                    out_scale=1.0, tok_index=None, k_row=0, v_row=0, pool=0, pool_base=0, v_shared=False, v_col=0, out_head=0):
     """Every token of the step (or those listed in tok_index) against the pages of its sequence: position i sees j <= i
     with i - j < window (0: all) or j < keep_first; sink [heads] f32 or None.  k_row / v_row: elements between the cache
     rows of neighbouring slots (0: kv_heads * dk / kv_heads * dv).  pool > 0: besides the window, one averaged entry per
     block of `pool` positions wholly before it, read from cache rows pool_base.. (`pool_blocks`).  v_shared: every head
-    reads value columns [0, dv) of a row — dv is then all value heads side by side.  An f32 `out` is written as f32 whatever
-    the activation type."""
+    reads value columns [v_col, v_col + dv) of a row — dv is then several (or all) value heads side by side, and out_head the
+    distance between the heads of an output row.  An f32 `out` is written as f32 whatever the activation type."""
     a = PagedAttentionArgs()
     a.k_row, a.v_row = int(k_row), int(v_row)
     a.pool, a.pool_base, a.v_shared = int(pool), int(pool_base), int(bool(v_shared))
     a.out_f32 = int(out.dtype == torch.float32 and y.dtype != torch.float32)
-    a.q, a.q_ld, a.k_cache, a.v_cache = _p(y, q_col).value, y.stride(0), k_cache.data_ptr(), v_cache.data_ptr()
+    a.q, a.q_ld, a.k_cache, a.v_cache = _p(y, q_col).value, y.stride(0), k_cache.data_ptr(), _p(v_cache, int(v_col)).value
+    a.out_head = int(out_head)
     a.dtype, a.heads, a.kv_heads, a.dk, a.dv = DTYPE_CODE[y.dtype], heads, kv_heads, dk, dv
     a.scale, a.window, a.keep_first, a.sink = scale, int(window), int(keep_first), _p(sink).value
     a.pages, a.pages_ld, a.page_size = batch.pages.data_ptr(), batch.pages.shape[1], page_size

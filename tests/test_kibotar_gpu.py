@@ -247,10 +247,14 @@ def test_mixers(cuda, layer, dtype, tol, portions):
                                    attn_layer(heads=8, kv_heads=1, dim=64, vdim=64, window=16, pool=16, rot_dims=64),
                                    attn_layer(heads=4, kv_heads=2, dim=16, vdim=136, window=7, pool=3, rot_dims=16, scaling={"factor": 3.0, "low": 0.5, "high": 2.0, "original": 16}),
                                    attn_layer(heads=12, kv_heads=4, dim=32, vdim=16, window=30, pool=7, rot_dims=8, base=50.0),
-                                   attn_layer(heads=2, kv_heads=2, dim=16, vdim=16, window=5, pool=40, rot_dims=4)])
+                                   attn_layer(heads=2, kv_heads=2, dim=16, vdim=16, window=5, pool=40, rot_dims=4),
+                                   attn_layer(heads=8, kv_heads=8, dim=16, vdim=136, window=9, pool=2, rot_dims=8),
+                                   attn_layer(heads=4, kv_heads=2, dim=16, vdim=600, window=9, pool=2, rot_dims=8),
+                                   attn_layer(heads=4, kv_heads=2, dim=16, vdim=24, window=0, pool=0, rot_dims=8)])
 def test_attention_other_sizes(cuda, layer):
     """One or all heads sharing keys, full / partial rotation, key size != value size, blocks of 1, blocks that do not divide a
-    page, blocks larger than a page, a block larger than the window, a window wider than the sequence."""
+    page, blocks larger than a page, a block larger than the window, a window wider than the sequence, value heads that together
+    are wider than one launch of the kernel takes, no window at all."""
     got, want = mixer_case(cuda, layer, torch.float32, 100, [25, 1, 1, 3, 30, 40], width=48)
     close_rows(got, want, 3e-5)
 
@@ -651,6 +655,19 @@ def test_bfloat16_model_on_tensor_cores(cuda):
     got = replay(eng, p, [[("a", 100), ("b", 45)], [("a", 1), ("b", 44), ("c", 39)], [("a", 99), ("b", 1), ("c", 1)]])
     for k in p:
         assert_close(got[k], P.forward(cj, w, p[k]).numpy(), torch.bfloat16, k)
+
+
+def test_without_pair_table_and_without_passes(cuda):
+    """The embedding's second table and the repeated range are options of the configuration: a model with neither."""
+    cj = make_cfg([gla_layer(mlp=DENSE), attn_layer(mlp=None)], emb=2.0)
+    cj["embedding"].pop("bigram")
+    model, w = build(cj, torch.float32, cuda, 23)
+    assert "bigram" not in w and "loop.step" not in w
+    p = {"x": tokens(60, 131, 8), "y": tokens(21, 131, 9)}
+    eng = engine.Engine(model, max_tokens=96, max_seqs=2)
+    got = replay(eng, p, [[("x", 30), ("y", 3)], [("x", 1), ("y", 18)], [("x", 29)]])
+    for k in p:
+        assert_close(got[k], P.forward(cj, w, p[k]).numpy(), torch.float32, k)
 
 
 def test_greedy_generation_through_the_scheduler(cuda):
