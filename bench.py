@@ -1078,7 +1078,8 @@ def bench_kibotar(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
     warmup, steps = max(3, warmup), max(1, steps)
     names = ["embed_scaled", "embed_pair", "streams_read_norm", "rms_residual", "glu_split", "gated_group_norm", "causal_conv", "linear_scan",
              "activate_cols", "bounded_gate", "power_gate", "latent_prepare", "rotate_pairs", "latent_prompt_attention", "paged_attention",
-             "prompt_attention", "attention_prepare", "rotation_table", "pool_blocks", "mix_heads", "gate_cols", "moe_route_scored", "moe_small",
+             "prompt_attention", "dense_prompt_attention", "attention_prepare", "rotation_table", "pool_blocks", "mix_heads", "gate_cols",
+             "moe_route_scored", "moe_small",
              "moe_sort", "moe_gather", "moe_combine", "scale_rows"]
     measure = engine_bench_tools(torch, dev, steps, warmup, prompt, decode_batches, names)
     out = {"metric": "kibotar_prefill_tok_s", "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True,
@@ -1124,11 +1125,19 @@ def bench_kibotar(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
                                   "like_hbm_frac": gbs(fprep, fops.get("latent_prepare", 0.0) + fops.get("rotate_pairs", 0.0))}
         lflop = 2 * 2.0 * H * (R + R) * (T * (T + 1) / 2)                   # two causal latent layers; per (query, key, head): dk + dv multiply-adds
         fflop = 2 * 2.0 * H * ((fR + fdr) + fR) * sum(min(i + 1, fwin) for i in range(T))
-        roof["latent_prompt_attention (causal)"] = {"ms": ops.get("latent_prompt_attention"), "tflops": tfl(lflop, ops.get("latent_prompt_attention")),
-                                                    "tensor_frac": (tfl(lflop, ops.get("latent_prompt_attention")) or 0.0) / tpeak,
-                                                    "like": "latent_prompt_attention (window %d)" % fwin, "like_ms": fops.get("latent_prompt_attention"),
-                                                    "like_tflops": tfl(fflop, fops.get("latent_prompt_attention")),
-                                                    "like_tensor_frac": (tfl(fflop, fops.get("latent_prompt_attention")) or 0.0) / tpeak}
+        if ops.get("dense_prompt_attention"):      # whole prompts: keys and values decompressed for the step, plain prompt kernel over dense rows
+            dflop = 2 * 2.0 * H * 2 * d * (T * (T + 1) / 2)                 # two causal layers; per (query, key, head): dk + dv multiply-adds
+            roof["dense_prompt_attention (latent layers, causal, decompressed)"] = {
+                "ms": ops.get("dense_prompt_attention"), "tflops": tfl(dflop, ops.get("dense_prompt_attention")),
+                "tensor_frac": (tfl(dflop, ops.get("dense_prompt_attention")) or 0.0) / tpeak, "absorbed_form_would_need_tflop": lflop / 1e12,
+                "like": "latent_prompt_attention (window %d, absorbed)" % fwin, "like_ms": fops.get("latent_prompt_attention"),
+                "like_tflops": tfl(fflop, fops.get("latent_prompt_attention")), "like_tensor_frac": (tfl(fflop, fops.get("latent_prompt_attention")) or 0.0) / tpeak}
+        else:
+            roof["latent_prompt_attention (causal)"] = {"ms": ops.get("latent_prompt_attention"), "tflops": tfl(lflop, ops.get("latent_prompt_attention")),
+                                                        "tensor_frac": (tfl(lflop, ops.get("latent_prompt_attention")) or 0.0) / tpeak,
+                                                        "like": "latent_prompt_attention (window %d)" % fwin, "like_ms": fops.get("latent_prompt_attention"),
+                                                        "like_tflops": tfl(fflop, fops.get("latent_prompt_attention")),
+                                                        "like_tensor_frac": (tfl(fflop, fops.get("latent_prompt_attention")) or 0.0) / tpeak}
         seen = sum(min(i + 1, win) + max(0, i - win + 1) // pool for i in range(T))
         aflop = 2.0 * H * 2 * d * seen                                       # per (query, key, head): dk + dv multiply-adds
         roof["prompt_attention (window + averaged blocks, once per value head)"] = {

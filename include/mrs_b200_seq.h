@@ -291,7 +291,9 @@ int mrs_seq_prompt_attention_pooled(const void *q, int64_t q_ld, const void *k_c
  *   cache[slot(t)][0 : kv_rank] = rms_norm(y[t][kv_col : kv_col + kv_rank]) * kv_norm_w   (the key/value latent)
  *   cache[slot(t)][kv_rank : kv_rank + rot_dim] = turn(y[t][kv_col + kv_rank : ...])     (the key part all heads share)
  * turn: entries (2i, 2i + 1), i < rot_dims / 2, rotate by cos_sin[t][i] (f32 [n_tok, rot_dims / 2, 2]); the rest pass.
- * cache rows are cache_row elements apart.  q_rank 0: no query part; kv_rank 0: no cache part. */
+ * cache rows are cache_row elements apart.  q_rank 0: no query part; kv_rank 0: no cache part.  kv_out (optional): the normed
+ * key/value latent also goes to kv_out[t][0 : kv_rank] (row stride kv_out_ld), for callers that decompress keys and values
+ * of the step's own tokens with a matrix product. */
 typedef struct {
   const void *y;
   int64_t y_ld;
@@ -308,6 +310,8 @@ typedef struct {
   int64_t cache_row;
   const int64_t *slot_of_tok;
   int n_tok;
+  void *kv_out;
+  int64_t kv_out_ld;
 } mrs_seq_latent_prepare_args;
 int mrs_seq_latent_prepare(const mrs_seq_latent_prepare_args *args, int64_t stream);
 /* out[t][h][0:dims] = in[t][h][0:dims] with entries (2i, 2i + 1), i < rot_dims / 2, rotated by cos_sin[t][i], the rest

@@ -38,7 +38,12 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const mrs_seq_laten
     ss = fmaf(v, v, ss);
   }
   const float inv = rsqrtf_exact(block_sum(ss, red) / (float)a.kv_rank + a.eps);
-  for (int c = threadIdx.x; c < a.kv_rank; c += blockDim.x) dst[c] = from_f32<T>(to_f32<T>(src[c]) * inv * a.kv_norm_w[c]);
+  T *dense = a.kv_out ? (T *)a.kv_out + (int64_t)t * a.kv_out_ld : nullptr;      // the normed latent also as a dense row of the step
+  for (int c = threadIdx.x; c < a.kv_rank; c += blockDim.x) {
+    const T r = from_f32<T>(to_f32<T>(src[c]) * inv * a.kv_norm_w[c]);
+    dst[c] = r;
+    if (dense) dense[c] = r;
+  }
   const int half = a.cos_sin ? a.rot_dims / 2 : 0;
   const float2 *cs = (const float2 *)a.cos_sin + (int64_t)t * half;
   src += a.kv_rank;

@@ -271,6 +271,11 @@ class LatentAttentionMixer:
     tensor-core latent kernel (all heads of a token share one fetched key tile); f32, and sizes the kernel does not take,
     run on the (token, head) kernel over the pages.  `shares`: this mixer has no W_dkv and reads the cache another layer fills.
 
+    When every sequence of a step starts in it with a long portion (whole prompts) and the sizes allow (bf16, no rotated part,
+    dn = dv of 64 or 128, at least DECOMPRESS_MIN_TOKENS tokens), keys and values ARE decompressed, for this step only: two
+    products turn the step's normed latents into per-head keys and values, and the plain tensor-core prompt kernel runs over
+    these dense rows — dn + dv multiply-adds per (query, key, head) instead of 2 kv_rank.  The cache still holds only latents.
+
     q_rank 0: there is no query latent — w_down's first heads * (dn + dr) rows are the query projection itself (w_uq and
     q_norm_w are None).  dr 0 with rotation None: no rotated part, scores carry no position.  `head_gate`: w_down ends with
     `heads` more rows, and head h's output is multiplied by that activation of row h's product (a gate per head)."""
@@ -279,6 +284,7 @@ class LatentAttentionMixer:
                  page_size, shares=False, head_gate=None):
         self.head_gate = head_gate
         self.w_down, self.w_uq, self.w_o, self.q_norm_w, self.kv_norm_w = w_down, w_uq, w_o, q_norm_w, kv_norm_w
+        self.w_uk_rows, self.w_uv_rows = w_uk, w_uv                      # [H dn, r] / [H dv, r]: the decompressing products
         self.w_uk = w_uk.view(heads, dn, kv_rank)                       # [H][dn][r]: q_plain,h @ w_uk[h] = W_uk,h^T q_plain,h
         self.w_uv_t = w_uv.view(heads, dv, kv_rank).transpose(1, 2)     # [H][r][dv]
         self.heads, self.dn, self.dr, self.dv, self.q_rank, self.kv_rank = heads, dn, dr, dv, q_rank, kv_rank
@@ -291,9 +297,30 @@ class LatentAttentionMixer:
         row = -(-self.row // 8) * 8            # rows start on 16-byte boundaries
         return {"latent": torch.zeros(n_token_slots, row, dtype=dtype, device=device)}
 
+    DECOMPRESS_MIN_TOKENS = 256
+
+    def decompresses(self, h, batch):
+        """True when this step's keys and values are decompressed (see the class text)."""
+        return (h.dtype == torch.bfloat16 and not self.shares and self.dr == 0 and self.dn == self.dv and self.dv in (64, 128) and
+                self.kv_rank % 8 == 0 and self.w_down.shape[0] % 8 == 0 and batch.n_seq > 0 and len(batch.long) == batch.n_seq and
+                all(past == 0 for _, _, past, _ in batch.long) and h.shape[0] >= self.DECOMPRESS_MIN_TOKENS)
+
     def forward(self, h, batch, cache):
         T, H, dn, dr, R = h.shape[0], self.heads, self.dn, self.dr, self.kv_rank
         latent = cache["latent"]
+        if self.decompresses(h, batch):
+            y = linear(h, self.w_down)
+            q_cols = self.q_rank if self.q_rank > 0 else H * dn
+            c = torch.empty(T, R, dtype=h.dtype, device=h.device)
+            cq = torch.empty(T, self.q_rank, dtype=h.dtype, device=h.device) if self.q_rank > 0 else None
+            K.latent_prepare(y, 0, self.q_rank, self.q_norm_w, cq, q_cols, R, 0, 0, self.kv_norm_w, None, self.eps, latent, batch.slot_of_tok, kv_out=c)
+            q2 = linear(cq, self.w_uq) if self.q_rank > 0 else y
+            out = torch.empty(T, H * self.dv, dtype=h.dtype, device=h.device)
+            K.dense_prompt_attention(q2, 0, linear(c, self.w_uk_rows), linear(c, self.w_uv_rows), batch, H, H, self.dv, self.scale, self.window,
+                                     None, out)
+            if self.head_gate is not None:
+                K.gate_cols(out, y, q_cols + R, H * self.dv, self.dv, self.head_gate)
+            return linear(out, self.w_o)
         cos_sin = self.rotation.table(batch) if self.rotation is not None else None
         rot_dims = self.rotation.dims if self.rotation is not None else 0
         y = linear(h, self.w_down)                                           # query latent (or queries) | (key/value latent | shared key part) | (gates)

@@ -83,7 +83,8 @@ class LatentPrepareArgs(ctypes.Structure):
                 ("q_norm_w", ctypes.c_void_p), ("q_out", ctypes.c_void_p), ("q_out_ld", ctypes.c_int64),
                 ("kv_col", ctypes.c_int), ("kv_rank", ctypes.c_int), ("rot_dim", ctypes.c_int), ("rot_dims", ctypes.c_int),
                 ("kv_norm_w", ctypes.c_void_p), ("cos_sin", ctypes.c_void_p), ("eps", ctypes.c_float), ("cache", ctypes.c_void_p),
-                ("cache_row", ctypes.c_int64), ("slot_of_tok", ctypes.c_void_p), ("n_tok", ctypes.c_int)]
+                ("cache_row", ctypes.c_int64), ("slot_of_tok", ctypes.c_void_p), ("n_tok", ctypes.c_int), ("kv_out", ctypes.c_void_p),
+                ("kv_out_ld", ctypes.c_int64)]
 
 class AttnPrepareArgs(ctypes.Structure):
     _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
@@ -428,6 +429,25 @@ def paged_attention(y, q_col, k_cache, v_cache, heads, kv_heads, dk, dv, scale, 
     _ok(lib().mrs_seq_paged_attention(ctypes.byref(a), _st(y)), "paged_attention")
 
 
+def dense_prompt_attention(q, q_col, k, v, batch, heads, kv_heads, d, scale, window, sink, out, out_col=0):
+    """The tensor-core prompt kernel over keys and values that are DENSE rows of the step (k, v [T, kv_heads * d], row t = the
+    step's token t) instead of pages: for steps whose sequences all start in this step with a long portion.  The kernel's page
+    table becomes one row per sequence listing its tokens' rows (page size 1); built once per step."""
+    if len(batch.long) != batch.n_seq or any(past for _, _, past, _ in batch.long):
+        raise ValueError("dense keys cover the step's own tokens only: every sequence must start in this step with a long portion")
+    plan = batch.__dict__.get("_dense_rows")
+    if plan is None:
+        rows = batch.long_rows.view(-1, 4)
+        table = (rows[:, 0:1] + torch.arange(batch.longest, dtype=torch.int32, device=rows.device)[None, :]).contiguous()
+        portions = rows.clone()
+        portions[:, 3] = torch.arange(rows.shape[0], dtype=torch.int32, device=rows.device)
+        plan = batch.__dict__["_dense_rows"] = (table, portions.contiguous())
+    table, portions = plan
+    _ok(lib().mrs_seq_prompt_attention_pooled(_p(q, q_col), _l(q.stride(0)), _p(k), _p(v), _p(out, out_col), _l(out.stride(0)), _p(portions),
+                                              _i(len(batch.long)), _i(batch.longest), _p(table), _i(table.shape[1]), _i(1), _i(heads), _i(kv_heads),
+                                              _i(d), _f(scale), _i(int(window)), _i(0), _p(sink), _i(0), _l(0), _i(0), _st(q)), "dense_prompt_attention")
+
+
 def pool_rows(n_token_slots, page_size, pool):
     """Cache rows that the averaged blocks of a pool of n_token_slots token rows need (per page: as many as blocks can start in one)."""
     return (n_token_slots // page_size) * (-(-page_size // pool))
@@ -552,9 +572,9 @@ def rms_residual(src, y=None, mult=1.0, dst=None, hist=None, n_hist=0, mix=None,
 
 
 # ---- attention through a shared latent -----------------------------------------------------------------------
-def latent_prepare(y, q_col, q_rank, q_norm_w, q_out, kv_col, kv_rank, rot_dim, rot_dims, kv_norm_w, cos_sin, eps, cache, slot_of_tok):
+def latent_prepare(y, q_col, q_rank, q_norm_w, q_out, kv_col, kv_rank, rot_dim, rot_dims, kv_norm_w, cos_sin, eps, cache, slot_of_tok, kv_out=None):
     """From the columns of y: q_out = rms_norm(query latent) * w; cache[slot] = rms_norm(key/value latent) * w | the shared key
-    part turned in neighbouring pairs.  kv_rank 0: only the query part."""
+    part turned in neighbouring pairs.  kv_rank 0: only the query part.  kv_out [T, >= kv_rank]: the normed latent also as dense rows."""
     a = LatentPrepareArgs()
     a.y, a.y_ld, a.dtype = _p(y).value, y.stride(0), DTYPE_CODE[y.dtype]
     a.q_col, a.q_rank, a.q_norm_w = int(q_col), int(q_rank), _p(q_norm_w).value
@@ -565,6 +585,8 @@ def latent_prepare(y, q_col, q_rank, q_norm_w, q_out, kv_col, kv_rank, rot_dim, 
     if kv_rank:
         a.cache, a.cache_row, a.slot_of_tok = _p(cache).value, cache.stride(0), _p(slot_of_tok).value
     a.n_tok = y.shape[0]
+    if kv_out is not None:
+        a.kv_out, a.kv_out_ld = _p(kv_out).value, kv_out.stride(0)
     _ok(lib().mrs_seq_latent_prepare(ctypes.byref(a), _st(y)), "latent_prepare")
 
 

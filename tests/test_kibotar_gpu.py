@@ -325,6 +325,35 @@ def test_latent_other_sizes(cuda, layer, dtype, tol):
     close_rows(got, want, tol)
 
 
+@pytest.mark.parametrize("layer", [latent_layer(heads=3, dim=64, vdim=64, kv_rank=40), latent_layer(heads=2, dim=128, vdim=128, kv_rank=264)])
+@pytest.mark.parametrize("portions", [[300], [300, 1, 1, 40], [257, 43]])
+def test_latent_whole_prompt_is_decompressed(cuda, layer, portions, monkeypatch):
+    """A step in which every sequence starts with a long portion decompresses keys and values for that step and runs the plain
+    tensor-core kernel over them; what follows (decoded tokens, later portions) reads the cached latents in the absorbed form."""
+    seen = []
+    real = K.dense_prompt_attention
+    monkeypatch.setattr(K, "dense_prompt_attention", lambda *a, **k: (seen.append(1), real(*a, **k))[1])
+    got, want = mixer_case(cuda, layer, torch.bfloat16, sum(portions), portions)
+    assert len(seen) == 1
+    close_rows(got, want, 3e-2)
+
+
+def test_latent_decompressed_for_two_prompts_at_once(cuda, monkeypatch):
+    layer = latent_layer(heads=3, dim=64, vdim=64, kv_rank=40)
+    cj = make_cfg([layer], width=64)
+    model, w = build(cj, torch.bfloat16, cuda, 7)
+    mixer = model.layers[0].mixer
+    cache = mixer.alloc_cache(2, 16 * 40, torch.bfloat16, cuda)
+    g = torch.Generator().manual_seed(7)
+    hs = [torch.randn(n, 64, generator=g).to(torch.bfloat16) for n in (200, 90)]
+    b = seq_batch(cuda, [(200, 0, 0, 1), (90, 0, 1, 20)])
+    assert mixer.decompresses(torch.cat(hs), b)
+    got = mixer.forward(torch.cat(hs).to(cuda).contiguous(), b, cache).double().cpu()
+    close_rows(got, torch.cat([plain_mixer(layer, h.double(), w, 1e-5) for h in hs]), 3e-2)
+    b2 = seq_batch(cuda, [(200, 0, 0, 1), (1, 90, 1, 20)])          # a decoded token beside a prompt: the absorbed form for both
+    assert not mixer.decompresses(torch.cat(hs), b2)
+
+
 @pytest.mark.parametrize("layer", [gla_layer(heads=1, dim=7, vdim=5, tau=1.0), gla_layer(heads=5, dim=136, vdim=24, tau=3.0),
                                    gla_layer(heads=2, dim=16, vdim=200, tau=64.0), gla_layer(heads=2, dim=600, vdim=8, tau=16.0)])
 def test_gla_other_sizes(cuda, layer):
