@@ -963,12 +963,12 @@ def kibotar_bench_config(width, vocab=32000):
     times the width; the last three layers form a repeated range of one pass (its step vector is added before it)."""
     H = width // 128
     lat = {"heads": H, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5}
-    att = {"heads": H, "kv_heads": max(1, H // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024, "pool": 8},
-           "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
-    gla = {"heads": H, "dim": 128, "vdim": 128, "tau": 16.0}
+    att = {"heads": H, "kv_heads": max(1, H // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024, "pool": 16},
+           "rot": {"base": 1000000.0, "dims": 128, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 4096}}}
+    gla = {"heads": H, "dim": 128, "vdim": 128, "tau": 8.0}
     mlp = {"kind": "dense", "ff": 4 * width}
-    return {"architecture": "Kibotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 127}},
+    return {"architecture": "Kibotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": width ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 4099, "mul_cur": 131}},
             "loop": {"start": 1, "stop": 4, "times": 1},
             "layers": [{"type": "latent_attention", "mixer": lat, "mlp": mlp}, {"type": "attention", "mixer": att, "mlp": mlp},
                        {"type": "gla", "mixer": gla, "mlp": mlp}, {"type": "latent_attention", "mixer": lat, "mlp": mlp}]}
@@ -1181,7 +1181,7 @@ def bench_kibotar(torch, dev, peaks, steps=3, warmup=3, widths=(2048, 4096), pro
         out["sizes"].append(row)
     out["value"] = out["sizes"][0]["prefill_tok_s"]
     out["ms_per_step"] = out["sizes"][0]["prefill_ms"]
-    out["config"] = {"workload": "4 layers (latent attention, attention over a window of 1024 plus averaged blocks of 8 with head-mixed weights, gated linear "
+    out["config"] = {"workload": "4 layers (latent attention, attention over a window of 1024 plus averaged blocks of 16 with head-mixed weights, gated linear "
                                  "attention, latent attention; dense feed-forwards of 4 x width), widths %s, %d-token prompt; decode at context %d; Fosulix at "
                                  "equal sizes beside it; L2 flushed between repetitions" % (list(widths), prompt, prompt // 8)}
     return out
